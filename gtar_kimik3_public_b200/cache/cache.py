@@ -11,8 +11,9 @@ fixed size per batch row (src/cache.py:48-57).  Here
   live sequences hold (each rounded up to a page) and not by slots times the longest context;
 * layers whose mixers ask for the same kind of storage form a *group* with tensors and a page
   pool of its own: one group for "all positions", one per window length (pages that have left
-  the window go back to the pool), one per shape of fixed-size state; a group's pages hold keys and
-  values per kv head, or one row per position for all heads (a layer that attends through a latent);
+  the window go back to the pool, except those of first positions that the request keeps), one per
+  shape of fixed-size state; a group's pages hold keys and values per kv head (values may have a width
+  of their own), or one row per position for all heads (a layer that attends through a latent);
 * stale data is never cleared from pages: nothing reads beyond a sequence's length (the
   reference argues the same for its rollback, src/cache.py:37-45).  State rows are zeroed when
   a slot is handed out.
@@ -68,9 +69,9 @@ class _KVGroup:
             self.k = torch.empty((len(items), n_pages, page_size, request.width), dtype=dtype, device=device)
             self.v = None
         else:
-            shape = (len(items), n_pages, request.n_kv_heads, page_size, request.head_dim)
-            self.k = torch.empty(shape, dtype=dtype, device=device)
-            self.v = torch.empty(shape, dtype=dtype, device=device)
+            shape = (len(items), n_pages, request.n_kv_heads, page_size)
+            self.k = torch.empty((*shape, request.head_dim), dtype=dtype, device=device)
+            self.v = torch.empty((*shape, request.value_dim or request.head_dim), dtype=dtype, device=device)
         self.pages = PageAllocator(n_pages)
         self.max_pages_per_seq = max_pages_per_seq
         self.table_host = np.zeros((n_slots, max_pages_per_seq), dtype=np.int32)
@@ -110,7 +111,9 @@ class _KVGroup:
                             f"({self.max_pages_per_seq * self.page_size})")
         owned = self.owned[slot]
         if self.request.window is not None:  # pages wholly before the window go back to the pool
-            gone = [i for i in owned if i < first]
+            kept = getattr(self.request, "keep_first", 0)
+            last_kept = (kept - 1) // self.page_size if kept > 0 else -1  # pages that hold the kept first positions stay
+            gone = [i for i in owned if last_kept < i < first]
             if gone:
                 self.pages.free([owned.pop(i) for i in gone])
         begin = max(first, self.upto[slot])
@@ -294,7 +297,7 @@ class Cache:
             if isinstance(r, RowsRequest):
                 total += len(group.items) * r.width * self.k_element_size()
             else:
-                total += 2 * len(group.items) * r.n_kv_heads * r.head_dim * self.k_element_size()
+                total += len(group.items) * r.n_kv_heads * (r.head_dim + (r.value_dim or r.head_dim)) * self.k_element_size()
         return total
 
     def k_element_size(self) -> int:

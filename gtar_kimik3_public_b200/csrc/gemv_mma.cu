@@ -171,6 +171,11 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
             if (p.swiglu == 2) {  // an activation of one number: applied where the sums are, then stored as any result
                 a = gelu_tanh(a);
                 b = gelu_tanh(b);
+            } else if (p.swiglu == 3) {  // the square of relu
+                a = fmaxf(a, 0.f);
+                b = fmaxf(b, 0.f);
+                a *= a;
+                b *= b;
             }
             if (p.resid) {
                 float* o = p.resid + (size_t)token * p.ldr + col;
@@ -503,7 +508,7 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
 
 // OUT[t, :] = x[t, :] @ w^T for 1 to 16 tokens (17 to 32 where 257 <= k <= 1024) and up to 64 weight rows per SM; `w` [n, k] and `x` [tokens, k]
 // bfloat16 with rows in steps of 8 elements (16 bytes); OUT bfloat16 or float32, [tokens, n], or with `swiglu` = 1
-// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows; `swiglu` = 2 stores gelu_tanh of every result.
+// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows; `swiglu` = 2 stores gelu_tanh of every result, 3 the square of its relu.
 GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const void* x, int tokens, long long ldx, void* out,
                            int out_dtype, int swiglu, void* stream) {
     GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 32, "gemv: takes 1 to 32 tokens and positive sizes; got %d tokens, n=%d k=%d",
@@ -512,7 +517,7 @@ GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const voi
                k, ldw, ldx);
     GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 3) == 0, "gemv: operands must be 16-byte aligned");
     GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemv: bad output dtype");
-    GK_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemv: output stage %d is none of store, SwiGLU, GELU", swiglu);
+    GK_REQUIRE(swiglu >= 0 && swiglu <= 3, "gemv: output stage %d is none of store, SwiGLU, GELU, squared relu", swiglu);
     GK_REQUIRE(swiglu != 1 || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");
     GemvParams p = {};
     p.w = (const __nv_bfloat16*)w;

@@ -430,11 +430,12 @@ def gemv_suits(m: int, n: int, k: int, device: torch.device) -> bool:
 
 
 def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
-         out: torch.Tensor | None = None, gelu: bool = False) -> torch.Tensor:
+         out: torch.Tensor | None = None, gelu: bool = False, relu_squared: bool = False) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` for up to 16 tokens (32 where ``gemv_suits`` says so): weights go from memory straight into registers and
     through ``mma.sync`` with 32-bit accumulation; made for the latency of a decode step, where a projection
     is a few megabytes of weights and next to no arithmetic.  ``swiglu`` as in ``gemm_tc``; ``gelu`` stores the tanh form
-    of GELU of every result (the 32-bit sums go through it before they are rounded)."""
+    of GELU of every result (the 32-bit sums go through it before they are rounded), ``relu_squared`` the square of its
+    relu."""
     require_device(x.device)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
@@ -446,15 +447,16 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.b
         raise KernelError(f"gemv takes up to {GEMV_MAX_TOKENS_SHORT_K} tokens, got {m}")
     if swiglu and n % 2:
         raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
-    if swiglu and gelu:
-        raise KernelError("one output stage at a time: SwiGLU or GELU")
+    if swiglu + gelu + relu_squared > 1:
+        raise KernelError("one output stage at a time: SwiGLU, GELU or squared relu")
     n_out = n // 2 if swiglu else n
     if out is None:
         out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
     _check(out, "out", out_dtype, 2)
     if tuple(out.shape) != (m, n_out):
         raise KernelError(f"out has shape {tuple(out.shape)}, expected {(m, n_out)}")
-    call("gk_gemv_bf16", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype), 2 if gelu else int(swiglu), stream_ptr())
+    call("gk_gemv_bf16", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype),
+         3 if relu_squared else 2 if gelu else int(swiglu), stream_ptr())
     return out
 
 
@@ -1470,4 +1472,182 @@ def experts_combine(y: torch.Tensor, place_of: torch.Tensor, weights: torch.Tens
     out = torch.empty((T, y.shape[1]), dtype=torch.float32, device=y.device)
     call("gk_experts_combine", ptr(y), dtype_code(y.dtype), ptr(place_of), ptr(weights), ptr(add), ptr(out), T, y.shape[1], top,
          stream_ptr())
+    return out
+
+
+# ------------------------------------------------------------------ layer norm, scored attention, linear attention with a fixed decay
+def add_layernorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                  rows: torch.Tensor | None = None, delta_scale: float = 1.0) -> torch.Tensor:
+    """``h += delta_scale * delta`` (in place, skipped when ``delta`` is None), then the layer norm of ``h`` with a weight
+    and no bias: ``(h - mean) / sqrt(mean((h - mean)^2) + eps) * weight``.  With ``rows`` (int32 indices) only those rows
+    are normed and ``h`` is not written."""
+    require_device(h.device)
+    _check(h, "h", torch.float32, 2)
+    _check(weight, "weight", dims=1)
+    hidden = h.shape[1]
+    if weight.shape[0] != hidden:
+        raise KernelError(f"norm weight has {weight.shape[0]} entries for rows of {hidden}")
+    delta_code = 0
+    if delta is not None:
+        _check(delta, "delta", dims=2)
+        if delta.shape != h.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+        delta_code = dtype_code(delta.dtype)
+    n_out = h.shape[0]
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_out = rows.shape[0]
+    out = torch.empty((n_out, hidden), dtype=out_dtype, device=h.device)
+    call("gk_add_layernorm", ptr(h), ptr(delta), delta_code, float(delta_scale), ptr(weight), dtype_code(weight.dtype), ptr(out),
+         dtype_code(out_dtype), ptr(rows), n_out, hidden, float(eps), stream_ptr())
+    return out
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float) -> torch.Tensor:
+    """``scale_a * a + scale_b * b`` in 32-bit, element by element."""
+    require_device(a.device)
+    _check(a, "a")
+    _check(b, "b", a.dtype)
+    if a.shape != b.shape:
+        raise KernelError(f"scaled_sum: {tuple(a.shape)} and {tuple(b.shape)}")
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    call("gk_scaled_sum", ptr(a), float(scale_a), ptr(b), float(scale_b), dtype_code(a.dtype), ptr(out), a.numel(), stream_ptr())
+    return out
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """``x <- factor * x`` in place (32-bit)."""
+    _check(x, "x", torch.float32)
+    call("gk_scale", ptr(x), x.numel(), float(factor), stream_ptr())
+    return x
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0)^2``, element by element."""
+    require_device(x.device)
+    _check(x, "x")
+    out = torch.empty_like(x)
+    call("gk_relu_squared", ptr(x), ptr(out), dtype_code(x.dtype), x.numel(), stream_ptr())
+    return out
+
+
+PREPARE_SILU_QK, PREPARE_SILU_V, PREPARE_UNIT_RMS = 1, 2, 4
+
+
+def heads_prepare(proj: torch.Tensor, q_at: int, k_at: int, v_at: int, n_q: int, n_k: int, d: int, dv: int, tok_pos: torch.Tensor,
+                  tok_seq: torch.Tensor, slots: torch.Tensor, *, silu_qk: bool = False, silu_v: bool = False, rot: int = 0,
+                  cos: torch.Tensor | None = None, sin: torch.Tensor | None = None, unit_eps: float | None = None,
+                  k_scale: float = 1.0, kv: PagedKV | None = None, write_kv: bool = True, max_position: int | None = None):
+    """What stands between a packed projection and a mixer's core.  ``proj [T, >= ...]`` holds ``n_q`` query heads of ``d``
+    from column ``q_at``, ``n_k`` key heads of ``d`` from ``k_at`` and ``n_k`` value heads of ``dv`` from ``v_at``.  In this
+    order: SiLU (``silu_qk`` on q and k, ``silu_v`` on v); rotation of the first ``rot`` entries of every q and k head by
+    the token's position (entry ``i`` with ``i + rot/2``; ``cos``, ``sin`` ``[positions, rot/2]``); with ``unit_eps`` every q
+    and k head divided by its root mean square; ``k_scale`` on k.  With ``kv`` the keys and values are written into the
+    cache's pages and q ``[T, n_q, d]`` comes back in the projection's type; without, q, k ``[T, n, d]`` and v ``[T, n_k,
+    dv]`` come back as 32-bit arrays."""
+    require_device(proj.device)
+    _check(proj, "proj", dims=2)
+    T = proj.shape[0]
+    if max(q_at + n_q * d, k_at + n_k * d, v_at + n_k * dv) > proj.shape[1]:
+        raise KernelError(f"heads_prepare: a projection of {proj.shape[1]} columns is too narrow for these heads")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    if rot:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError(f"heads_prepare: tables of {cos.shape[1]} angles for {rot} rotated entries")
+        if max_position is not None and cos.shape[0] <= max_position:
+            raise KernelError(f"heads_prepare: tables hold {cos.shape[0]} positions, the step reaches {max_position}")
+    flags = (PREPARE_SILU_QK if silu_qk else 0) | (PREPARE_SILU_V if silu_v else 0) | (PREPARE_UNIT_RMS if unit_eps is not None else 0)
+    dev = proj.device
+    if kv is not None:
+        _check(kv.k, "k pages", proj.dtype, 4)
+        _check(kv.v, "v pages", proj.dtype, 4)
+        if tuple(kv.k.shape[1:]) != (n_k, kv.page_size, d) or tuple(kv.v.shape[1:]) != (n_k, kv.page_size, dv):
+            raise KernelError(f"heads_prepare: pages {tuple(kv.k.shape)} / {tuple(kv.v.shape)} do not hold {n_k} heads of {d} / {dv}")
+        q = torch.empty((T, n_q, d), dtype=proj.dtype, device=dev)
+        call("gk_heads_prepare", ptr(proj), dtype_code(proj.dtype), proj.shape[1], q_at, k_at, v_at, n_q, n_k, d, dv, flags, rot,
+             ptr(cos) if rot else None, ptr(sin) if rot else None, float(unit_eps or 0.0), float(k_scale), ptr(tok_pos), ptr(tok_seq),
+             ptr(slots), ptr(q), dtype_code(q.dtype), None, None, ptr(kv.k), ptr(kv.v), ptr(kv.block_table), kv.max_pages,
+             kv.page_size, int(write_kv), T, stream_ptr())
+        return q
+    q = torch.empty((T, n_q, d), dtype=torch.float32, device=dev)
+    k = torch.empty((T, n_k, d), dtype=torch.float32, device=dev)
+    v = torch.empty((T, n_k, dv), dtype=torch.float32, device=dev)
+    call("gk_heads_prepare", ptr(proj), dtype_code(proj.dtype), proj.shape[1], q_at, k_at, v_at, n_q, n_k, d, dv, flags, rot,
+         ptr(cos) if rot else None, ptr(sin) if rot else None, float(unit_eps or 0.0), float(k_scale), ptr(tok_pos), ptr(tok_seq),
+         ptr(slots), ptr(q), dtype_code(q.dtype), ptr(k), ptr(v), None, None, None, 0, 0, 0, T, stream_ptr())
+    return q, k, v
+
+
+def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+               slots: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    """The recurrence ``S <- decay_h S + k v^T; o = S^T q`` over the step's tokens of every sequence, from and to
+    ``state [slots, heads, d, dv]`` (32-bit).  q, k ``[T, heads, d]``, v ``[T, heads, dv]``, ``decay [heads]``, all 32-bit.
+    Returns ``o [T, heads, dv]`` (32-bit)."""
+    require_device(q.device)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check(t, name, torch.float32, 3)
+    _check(decay, "decay", torch.float32, 1)
+    _check(state, "state", torch.float32, 4)
+    T, n_heads, d = q.shape
+    dv = v.shape[2]
+    if k.shape != q.shape or tuple(v.shape[:2]) != (T, n_heads) or tuple(state.shape[1:]) != (n_heads, d, dv) or decay.shape[0] != n_heads:
+        raise KernelError("decay_scan: the state, the decays or the inputs have other sizes than the heads")
+    out = torch.empty((T, n_heads, dv), dtype=torch.float32, device=q.device)
+    call("gk_decay_scan", ptr(q), ptr(k), ptr(v), ptr(decay), ptr(state), ptr(out), ptr(cu_q), ptr(slots), int(n_seqs), n_heads, d, dv,
+         stream_ptr())
+    return out
+
+
+def group_norm_gate(x: torch.Tensor, group: int, weight: torch.Tensor | None, gate: torch.Tensor, gate_at: int, eps: float,
+                    out_dtype: torch.dtype, gate_kind: str = "sigmoid") -> torch.Tensor:
+    """Rows of ``x [T, width]`` (32-bit) cut into groups of ``group`` entries; every group divided by its root mean square
+    (eps inside the root), multiplied by ``weight [group]`` (if given) and by sigmoid or SiLU of
+    ``gate[:, gate_at : gate_at + width]``.  Returns ``[T, width]`` in ``out_dtype``."""
+    require_device(x.device)
+    _check(x, "x", torch.float32, 2)
+    _check(gate, "gate", dims=2)
+    T, width = x.shape
+    if width % group or gate.shape[1] < gate_at + width or gate.shape[0] != T:
+        raise KernelError("group_norm_gate: the groups or the gate do not fit the rows")
+    if weight is not None:
+        _check(weight, "weight", torch.float32, 1)
+        if weight.shape[0] != group:
+            raise KernelError(f"group_norm_gate: a weight of {weight.shape[0]} for groups of {group}")
+    kinds = {"sigmoid": 0, "silu": 1}
+    out = torch.empty((T, width), dtype=out_dtype, device=x.device)
+    call("gk_group_norm_gate", ptr(x), ptr(weight), gate.data_ptr() + gate_at * gate.element_size(), dtype_code(gate.dtype),
+         gate.shape[1], ptr(out), dtype_code(out_dtype), T, width // group, group, float(eps), kinds[gate_kind], stream_ptr())
+    return out
+
+
+def attention_scored_exact(q: torch.Tensor, kv: PagedKV, tok_pos: torch.Tensor, tok_seq: torch.Tensor, slots: torch.Tensor,
+                           scale: float, window: int = 0, keep_first: int = 0, r1: torch.Tensor | None = None,
+                           r2: torch.Tensor | None = None, head_bias: torch.Tensor | None = None,
+                           weights: str = "softmax") -> torch.Tensor:
+    """Causal grouped-query attention of ``q [T, n_q, d]`` over pages of keys ``[.., d]`` and values ``[.., dv]`` (exact
+    kernel): a key at ``j`` is seen from ``i`` if ``i - j < window`` or ``j < keep_first``; the score is ``q . k * scale -
+    r1_h ln(1 + r2_h (i - j))``; the weights are the softmax over the seen keys, or ``sigmoid(score + head_bias_h)``
+    without a sum that divides.  Returns ``[T, n_q, dv]``."""
+    require_device(q.device)
+    _check(q, "q", dims=3)
+    n, n_q, d = q.shape
+    _check(kv.k, "k pages", q.dtype, 4)
+    _check(kv.v, "v pages", q.dtype, 4)
+    n_kv, dv = kv.k.shape[1], kv.v.shape[3]
+    if kv.k.shape[3] != d:
+        raise KernelError(f"pages have keys of {kv.k.shape[3]}, queries of {d}")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    for name, t in (("r1", r1), ("r2", r2), ("head_bias", head_bias)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != n_q:
+                raise KernelError(f"{name} has {t.shape[0]} entries for {n_q} query heads")
+    out = torch.empty((n, n_q, dv), dtype=q.dtype, device=q.device)
+    call("gk_attention_scored_exact", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), dtype_code(q.dtype), ptr(tok_pos), ptr(tok_seq),
+         ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, dv, kv.max_pages, kv.page_size, float(scale), int(window),
+         int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), {"softmax": 0, "sigmoid": 1}[weights], stream_ptr())
     return out

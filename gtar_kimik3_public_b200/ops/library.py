@@ -79,6 +79,14 @@ _SIGNATURES: dict[str, list] = {
     "gk_wide_norm_rope_write": [P, I, L, P, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "gk_sigmoid_gate": [P, P, L, P, I, L, I, P],
     "gk_softcap": [P, L, F, P],
+    "gk_add_layernorm": [P, P, I, F, P, I, P, I, P, I, I, F, P],
+    "gk_scaled_sum": [P, F, P, F, I, P, L, P],
+    "gk_relu_squared": [P, P, I, L, P],
+    "gk_scale": [P, L, F, P],
+    "gk_heads_prepare": [P, I, L, I, I, I, I, I, I, I, I, I, P, P, F, F, P, P, P, P, I, P, P, P, P, P, I, I, I, I, P],
+    "gk_decay_scan": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "gk_group_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, I, P],
+    "gk_attention_scored_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, I, P],
 }
 
 

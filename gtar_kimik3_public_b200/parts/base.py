@@ -44,11 +44,14 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Keys and values per position.  ``window`` = None keeps all positions."""
+    """Keys and values per position.  ``window`` = None keeps all positions; with a window, the first ``keep_first``
+    positions stay readable after the window has left them.  ``value_dim`` = None: values as wide as keys."""
 
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

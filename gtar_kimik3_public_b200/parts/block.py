@@ -1,6 +1,8 @@
 """Pre-norm residual block: ``h += mixer(norm_in(h)); h += ffn(norm_post(h))``
 (src/models/transformer.py:47-48).  The adds are fused into the norm that follows them: the
-block hands its last branch output on as ``pending`` instead of adding it itself."""
+block hands its last branch output on as ``pending`` instead of adding it itself.  Beside it: the block with
+convolutions over time in front of its sublayers, the block whose branches share one norm, and the block that norms
+every branch on both sides."""
 
 from __future__ import annotations
 
@@ -86,6 +88,112 @@ class PreNormBlock(Block):
 
 
 register_part("block", "pre_norm", PreNormBlock)
+
+
+class ConvPreNormBlock(Block):
+    """Pre-norm residual block whose sublayers read their input through a short causal convolution over time:
+
+        a = norm_1(x);  a += conv_1(a);  x += m * mixer(a)
+        b = norm_2(x);  b += conv_2(b);  x += m * feed_forward(b)            (left out for a layer without feed-forward)
+
+    ``conv``: ``taps`` taps per channel, no bias, zeros before the sequence's start; tap ``j`` multiplies the input
+    ``taps - 1 - j`` positions back.  The last ``taps - 1`` inputs of each convolution are part of a sequence's state, beside
+    what the mixer keeps.  The constant ``m`` on the branches belongs to the norms, which add a pending branch into the
+    stream (``delta_scale``): the norm after a branch, the next layer's first norm or the model's last.  The norms'
+    results feed the convolutions in 32-bit; the convolutions hand on the run's type.
+    """
+
+    def __init__(self, width: int, norm_1: Norm, mixer: Mixer, norm_2: Norm | None, feed_forward: FeedForward | None,
+                 conv_taps: int = 0, names: dict[str, str] | None = None):
+        if (feed_forward is None) != (norm_2 is None):
+            raise ValueError("a feed-forward comes with the norm before it, or not at all")
+        self.width, self.conv_taps = int(width), int(conv_taps)
+        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
+        self.names = {"mixer": "mix.", "feed_forward": "mlp.", "conv_1": "canon1", "conv_2": "canon2", **(names or {})}
+        self.conv_1 = self.conv_2 = None
+
+    def children(self):
+        parts = [("", self.norm_1), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            parts += [("", self.norm_2), (self.names["feed_forward"], self.feed_forward)]
+        return parts
+
+    def _own_specs(self):
+        from .base import TensorSpec
+
+        if not self.conv_taps:
+            return {}
+        keys = ["conv_1"] + (["conv_2"] if self.feed_forward is not None else [])
+        return {self.names[k]: TensorSpec((self.width, self.conv_taps), "matrix", init=(0.0, 0.3)) for k in keys}
+
+    def tensor_specs(self):
+        specs = {prefix + name: spec for prefix, part in self.children() for name, spec in part.tensor_specs().items()}
+        specs.update(self._own_specs())
+        return specs
+
+    def load(self, tensors):
+        for prefix, part in self.children():
+            part.load({name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors})
+        if self.conv_taps:
+            # [taps, width]: the kernels read tap by tap
+            self.conv_1 = tensors[self.names["conv_1"]].float().t().contiguous()
+            if self.feed_forward is not None:
+                self.conv_2 = tensors[self.names["conv_2"]].float().t().contiguous()
+
+    def weight_bytes(self):
+        own = sum(t.numel() * t.element_size() for t in (self.conv_1, self.conv_2) if t is not None)
+        return own + sum(part.weight_bytes() for _, part in self.children())
+
+    def n_conv_states(self) -> int:
+        if self.conv_taps <= 1:
+            return 0
+        return 2 if self.feed_forward is not None else 1
+
+    def cache_request(self):
+        request = self.mixer.cache_request()
+        n_own = self.n_conv_states()
+        if not n_own:
+            return request
+        from .base import StateRequest
+
+        own = [StateRequest((self.conv_taps - 1, self.width), torch.float32)] * n_own
+        if request is None:
+            return own
+        return [*request, *own] if isinstance(request, (list, tuple)) else [request, *own]
+
+    def _through_conv(self, a, weight, state, ctx: StepContext):
+        keep = state is not None and not ctx.extras.get("cache_read_only", False)
+        # one token a sequence: the convolution's kernel moves the states on itself
+        g = F.causal_conv(a, weight, state, ctx.tok_pos, ctx.tok_seq, ctx.cu_q, ctx.slots, ctx.dtype,
+                          update_single_token_state=keep and ctx.all_single)
+        if keep and not ctx.all_single:
+            F.conv_state(a, state, ctx.cu_q, ctx.slots, ctx.n_seqs)
+        return g
+
+    def forward(self, h, pending, ctx: StepContext, cache):
+        states = [None, None]
+        n_own = self.n_conv_states()
+        if n_own:
+            mixer_request = self.mixer.cache_request()
+            *views, = cache
+            states[:n_own] = views[len(views) - n_own:]
+            views = views[:len(views) - n_own]
+            cache = tuple(views) if isinstance(mixer_request, (list, tuple)) else (views[0] if views else None)
+        if self.conv_taps:
+            a = self._through_conv(self.norm_1.forward(h, pending, torch.float32), self.conv_1, states[0], ctx)
+        else:
+            a = self.norm_1.forward(h, pending, ctx.dtype)
+        branch = self.mixer.forward(a, ctx, cache)
+        if self.feed_forward is None:
+            return h, branch
+        if self.conv_taps:
+            b = self._through_conv(self.norm_2.forward(h, branch, torch.float32), self.conv_2, states[1], ctx)
+        else:
+            b = self.norm_2.forward(h, branch, ctx.dtype)
+        return h, self.feed_forward.forward(b, ctx)
+
+
+register_part("block", "pre_norm_conv", ConvPreNormBlock)
 
 
 class ParallelBlock(Block):

@@ -33,12 +33,13 @@ class OutputHead(Part):
     graph_safe = True
 
     """Logits in float32.  ``tied_to`` names an embedding whose table is used instead of an own matrix.  ``softcap``:
-    the logits become ``softcap * tanh(logits / softcap)`` (None: they stay as they are)."""
+    the logits become ``softcap * tanh(logits / softcap)`` (None: they stay as they are).  ``scale``: a constant on
+    the logits (applied to the 32-bit products, before a cap)."""
 
     def __init__(self, hidden_size: int, vocab_size: int, tied_to: TokenEmbedding | None = None, weight_name: str = "weight",
-                 softcap: float | None = None):
+                 softcap: float | None = None, scale: float = 1.0):
         self.hidden_size, self.vocab_size, self.tied_to = int(hidden_size), int(vocab_size), tied_to
-        self.weight_name, self.softcap = weight_name, (None if softcap is None else float(softcap))
+        self.weight_name, self.softcap, self.scale = weight_name, (None if softcap is None else float(softcap)), float(scale)
         self._weight: torch.Tensor | None = None
 
     def tensor_specs(self):
@@ -59,4 +60,6 @@ class OutputHead(Part):
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
         logits = linear(z, self.weight, torch.float32)
+        if self.scale != 1.0:
+            logits = F.scale_(logits, self.scale)
         return F.softcap_(logits, self.softcap) if self.softcap is not None else logits

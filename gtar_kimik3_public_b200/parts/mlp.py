@@ -85,3 +85,32 @@ class GeluFeedForward(FeedForward):
 
 
 register_part("feed_forward", "gelu", GeluFeedForward)
+
+
+class ReluSquaredFeedForward(FeedForward):
+    """``down(relu(up(x))^2)``: no gate, no biases.  The activation is the output stage of the few-token product and a
+    kernel of its own behind the many-token product."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, up_name: str = "up.weight", down_name: str = "down.weight"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.up_name: TensorSpec((i, h)), self.down_name: TensorSpec((h, i))}
+
+    def load(self, tensors):
+        self.w_up = tensors[self.up_name].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+        return linear(linear(x, self.w_up, relu_squared=True), self.w_down)
+
+
+register_part("feed_forward", "relu_squared", ReluSquaredFeedForward)

@@ -1,5 +1,6 @@
-"""RMSNorm: ``weight * (x * rsqrt(mean(x^2) + eps))`` in 32-bit (src/layers/rmsnorm.py:11-16),
-fused with the add of a pending branch output into the residual stream."""
+"""The norms that read the residual stream, each fused with the add of a pending branch output into it: RMSNorm,
+``weight * (x * rsqrt(mean(x^2) + eps))`` in 32-bit (src/layers/rmsnorm.py:11-16), and layer norm with a weight and no
+bias."""
 
 from __future__ import annotations
 
@@ -43,3 +44,30 @@ class RMSNorm(Norm):
 
 
 register_part("norm", "rmsnorm", RMSNorm)
+
+
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias, ``(x - mean) / sqrt(mean((x - mean)^2) + eps) * weight`` in 32-bit, fused with
+    the add of a pending branch output into the stream; ``delta_scale`` multiplies that branch as it is added (a model
+    that scales every branch by one constant gives it to all its norms)."""
+
+    graph_safe = True
+
+    def __init__(self, size: int, eps: float, weight_name: str = "weight", delta_scale: float = 1.0):
+        self.size, self.eps, self.weight_name, self.delta_scale = int(size), float(eps), weight_name, float(delta_scale)
+        self.weight: torch.Tensor | None = None
+
+    def tensor_specs(self):
+        return {self.weight_name: TensorSpec((self.size,), "vector")}
+
+    def load(self, tensors):
+        self.weight = tensors[self.weight_name].float().contiguous()
+
+    def weight_bytes(self):
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, h, delta, out_dtype, rows=None):
+        return F.add_layernorm(h, delta, self.weight, self.eps, out_dtype, rows, self.delta_scale)
+
+
+register_part("norm", "layernorm", LayerNorm)

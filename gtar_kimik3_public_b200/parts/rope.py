@@ -18,20 +18,25 @@ from .base import PositionEncoding, register_part
 class RotaryEncoding(PositionEncoding):
     graph_safe = True
 
-    def __init__(self, dim: int, base: float, precise: bool = False):
+    def __init__(self, dim: int, base: float, precise: bool = False, divisor: float = 1.0):
         """``precise``: frequencies, angles, cosines and sines are formed in 64-bit and rounded once to the 32-bit
-        tables (the default forms them in 32-bit, as the reference does)."""
+        tables (the default forms them in 32-bit, as the reference does).  ``divisor``: every frequency is divided by
+        it (linear scaling of positions; 1 leaves them as they are)."""
         if dim % 2:
             raise ValueError(f"rotary dimension must be even, got {dim}")
         self.dim = int(dim)
         self.base = float(base)
         self.precise = bool(precise)
+        self.divisor = float(divisor)
+        if not self.divisor > 0:
+            raise ValueError("the frequency divisor must be positive")
         self.cos: torch.Tensor | None = None
         self.sin: torch.Tensor | None = None
         self._replaced: list[torch.Tensor] = []  # shorter tables of before: captured launches may still read them
 
     def inv_freq(self) -> torch.Tensor:
-        return 1.0 / (self.base ** (torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim))
+        plain = 1.0 / (self.base ** (torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim))
+        return plain / self.divisor if self.divisor != 1.0 else plain
 
     def magnitude(self) -> float:
         """A factor on every cosine and sine (1 for the plain rotation)."""
@@ -47,7 +52,7 @@ class RotaryEncoding(PositionEncoding):
             self._replaced += [self.cos, self.sin]
         n = max(max_position + 1, 2 * have, 64)
         if self.precise:
-            inv = self.base ** (-torch.arange(0, self.dim, 2, dtype=torch.float64) / self.dim)
+            inv = self.base ** (-torch.arange(0, self.dim, 2, dtype=torch.float64) / self.dim) / self.divisor
             freqs = torch.arange(n, dtype=torch.float64)[:, None] * inv[None, :]
             self.cos = (freqs.cos() * self.magnitude()).float().to(device).contiguous()
             self.sin = (freqs.sin() * self.magnitude()).float().to(device).contiguous()

@@ -76,3 +76,7 @@ def _ensure_builtin() -> None:
     from .models.pofadra import build_pofadra_plan
 
     register_architecture(PofadraConfig.ARCH_NAMES, PofadraConfig, build_pofadra_plan)
+    from .config.rezulorn import RezulornConfig
+    from .models.rezulorn import build_rezulorn_plan
+
+    register_architecture(RezulornConfig.ARCH_NAMES, RezulornConfig, build_rezulorn_plan)
