@@ -1651,3 +1651,51 @@ def attention_scored_exact(q: torch.Tensor, kv: PagedKV, tok_pos: torch.Tensor, 
          ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, dv, kv.max_pages, kv.page_size, float(scale), int(window),
          int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), {"softmax": 0, "sigmoid": 1}[weights], stream_ptr())
     return out
+
+
+def scored_attention_parts(n_seqs: int, n_q: int, n_kv: int, max_q_len: int, visible_pages: int, n_sms: int) -> int:
+    """Into how many parts :func:`attention_scored` cuts the walk over a block's pages: one where the rows alone fill the
+    GPU twice over, else as many as bring the blocks there, and never more than the pages that a row can see."""
+    row_blocks = -(-max_q_len * (n_q // n_kv) // 64)
+    blocks = max(1, n_seqs * n_kv * row_blocks)
+    if blocks >= 2 * n_sms:
+        return 1
+    return max(1, min(-(-2 * n_sms // blocks), visible_pages, 32))
+
+
+def attention_scored(q: torch.Tensor, kv: PagedKV, cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, max_q_len: int,
+                     scale: float, window: int = 0, keep_first: int = 0, r1: torch.Tensor | None = None,
+                     r2: torch.Tensor | None = None, head_bias: torch.Tensor | None = None, weights: str = "softmax",
+                     n_parts: int = 1) -> torch.Tensor:
+    """:func:`attention_scored_exact` on the tensor cores: bfloat16, keys and values of 64 or 128 entries both, pages of 64
+    keys.  The new tokens ``q [n_tokens, n_q, d]`` are packed by sequence (``cu_q``), ``kv_len`` counts each sequence's
+    cached tokens including them.  ``n_parts`` > 1 cuts every block's keys into that many blocks whose sums a second
+    kernel adds (steps of few tokens)."""
+    require_device(q.device)
+    _check(q, "q", torch.bfloat16, 3)
+    n, n_q, d = q.shape
+    _check(kv.k, "k pages", torch.bfloat16, 4)
+    _check(kv.v, "v pages", torch.bfloat16, 4)
+    if kv.k.shape[3] != d or kv.v.shape[3] != d:
+        raise KernelError(f"attention_scored: pages of {kv.k.shape[3]} / {kv.v.shape[3]} for queries of {d} (use the exact kernel)")
+    for name, t in (("cu_q", cu_q), ("kv_len", kv_len), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    n_seqs = kv_len.shape[0]
+    if cu_q.shape[0] != n_seqs + 1 or slots.shape[0] != n_seqs:
+        raise KernelError("cu_q needs n_seqs + 1 entries, slots and kv_len n_seqs")
+    for name, t in (("r1", r1), ("r2", r2), ("head_bias", head_bias)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != n_q:
+                raise KernelError(f"{name} has {t.shape[0]} entries for {n_q} query heads")
+    sigmoid = {"softmax": 0, "sigmoid": 1}[weights]
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if n_parts > 1:
+        part_o = torch.empty((n_parts, n, n_q, d), dtype=torch.float32, device=q.device)
+        if not sigmoid:
+            part_ml = torch.empty((n_parts, n, n_q, 2), dtype=torch.float32, device=q.device)
+    call("gk_attention_scored_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(part_o), ptr(part_ml), ptr(cu_q), ptr(kv_len),
+         ptr(slots), ptr(kv.block_table), n_seqs, int(max_q_len), n, n_q, kv.k.shape[1], d, kv.max_pages, kv.page_size, float(scale),
+         int(window), int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), sigmoid, int(n_parts), stream_ptr())
+    return out

@@ -15,7 +15,9 @@ chooses what happens around the scores:
   ``sigmoid(score + pb_h)`` with a number per query head (tensor ``pb``, with ``head_bias``), and no sum over keys divides.
 
 Scores, weights and the sums over keys are 32-bit.  A step's kernels: the packed projection q | k | v; one kernel for
-rotation, unit lengths and the cache write; attention over the pages; the output projection.
+rotation, unit lengths and the cache write; attention over the pages (on the tensor cores in bfloat16 with keys and
+values of 64 or 128 entries, where steps of few tokens are cut over the keys into parts; else the exact kernel); the
+output projection.
 """
 
 from __future__ import annotations
@@ -92,8 +94,16 @@ class ScoredAttention(Mixer):
         q = F.heads_prepare(proj, 0, nq, nq + nk, self.n_q, self.n_kv, self.d, self.dv, ctx.tok_pos, ctx.tok_seq, ctx.slots,
                             rot=self.rot, cos=cos, sin=sin, unit_eps=self.norm_eps if self.unit_qk else None, kv=cache,
                             write_kv=write, max_position=ctx.max_position)
-        o = F.attention_scored_exact(q, cache, ctx.tok_pos, ctx.tok_seq, ctx.slots, self.scale, self.window or 0, self.keep_first,
-                                     self.r1, self.r2, self.pb, self.weights)
+        if q.dtype == torch.bfloat16 and self.d == self.dv and self.d in (64, 128) and cache.page_size == 64:
+            # what a row can see at most, whatever the lengths of later steps that replay this one from a graph
+            seen = -(-(self.window + self.keep_first) // 64) + 2 if self.window else cache.max_pages
+            parts = F.scored_attention_parts(ctx.n_seqs, self.n_q, self.n_kv, ctx.max_q_len, min(seen, cache.max_pages),
+                                             F.sm_count(q.device))
+            o = F.attention_scored(q, cache, ctx.cu_q, ctx.kv_len, ctx.slots, ctx.max_q_len, self.scale, self.window or 0,
+                                   self.keep_first, self.r1, self.r2, self.pb, self.weights, parts)
+        else:  # 32-bit runs and other head sizes
+            o = F.attention_scored_exact(q, cache, ctx.tok_pos, ctx.tok_seq, ctx.slots, self.scale, self.window or 0,
+                                         self.keep_first, self.r1, self.r2, self.pb, self.weights)
         return linear(o.view(ctx.n_tokens, self.n_q * self.dv), self.w_o)
 
 

@@ -114,26 +114,50 @@ def _visible(T: int, mask: dict | None) -> torch.Tensor:
     return seen
 
 
+def visible(T: int, mask: dict | None) -> torch.Tensor:
+    return _visible(T, mask)
+
+
+def softmax_core(q, k, v, scale: float, mask: dict | None, r1=None, r2=None) -> torch.Tensor:
+    """q [T, H, d], k [T, G, d], v [T, G, dv] -> [T, H, dv]: softmax over the visible keys of
+    q . k * scale - r1_h ln(1 + r2_h (i - j))."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    seen = _visible(T, mask)
+    i = torch.arange(T, dtype=q.dtype)
+    gap = (i[:, None] - i[None, :]).clamp_min(0.0)
+    outs = []
+    for head in range(H):
+        kh = head // (H // G)
+        s = (q[:, head] @ k[:, kh].T) * scale
+        if r1 is not None:
+            s = s - r1[head] * torch.log1p(r2[head] * gap)
+        s = s.masked_fill(~seen, -math.inf)
+        outs.append(torch.softmax(s, -1) @ v[:, kh])
+    return torch.stack(outs, 1)
+
+
+def sigmoid_core(q, k, v, scale: float, mask: dict | None, pb) -> torch.Tensor:
+    """The same shapes: a visible key's weight is sigmoid(q . k * scale + pb_h); nothing divides."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    seen = _visible(T, mask)
+    outs = []
+    for head in range(H):
+        kh = head // (H // G)
+        s = (q[:, head] @ k[:, kh].T) * scale + pb[head]
+        outs.append(torch.sigmoid(s).masked_fill(~seen, 0.0) @ v[:, kh])
+    return torch.stack(outs, 1)
+
+
 def biased_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
     """Softmax attention without rotation: score minus r1 ln(1 + r2 (i - j)); a sliding window that keeps the
     first tokens."""
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    q = mm(h, w[p + "q"].T).view(T, H, d)
-    k = mm(h, w[p + "k"].T).view(T, G, d)
+    q = turn(mm(h, w[p + "q"].T).view(T, H, d), m.get("rot"))
+    k = turn(mm(h, w[p + "k"].T).view(T, G, d), m.get("rot"))
     v = mm(h, w[p + "v"].T).view(T, G, dv)
-    seen = _visible(T, m.get("mask"))
-    i = torch.arange(T, dtype=h.dtype)
-    gap = (i[:, None] - i[None, :]).clamp_min(0.0)
-    outs = []
-    for head in range(H):
-        kh = head // (H // G)
-        s = (q[:, head] @ k[:, kh].T) * m["scale"]
-        if p + "r1" in w:
-            s = s - w[p + "r1"][head] * torch.log1p(w[p + "r2"][head] * gap)
-        s = s.masked_fill(~seen, -math.inf)
-        outs.append(torch.softmax(s, -1) @ v[:, kh])
-    return mm(torch.stack(outs, 1).reshape(T, H * dv), w[p + "o"].T)
+    o = softmax_core(q, k, v, m["scale"], m.get("mask"), w.get(p + "r1"), w.get(p + "r2"))
+    return mm(o.reshape(T, H * dv), w[p + "o"].T)
 
 
 def sigmoid_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
@@ -144,20 +168,14 @@ def sigmoid_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> 
     q = rms(turn(mm(h, w[p + "q"].T).view(T, H, d), m.get("rot")), eps)
     k = rms(turn(mm(h, w[p + "k"].T).view(T, G, d), m.get("rot")), eps)
     v = mm(h, w[p + "v"].T).view(T, G, dv)
-    seen = _visible(T, m.get("mask"))
-    outs = []
-    for head in range(H):
-        kh = head // (H // G)
-        s = (q[:, head] @ k[:, kh].T) * m["scale"] + w[p + "pb"][head]
-        weight = torch.sigmoid(s).masked_fill(~seen, 0.0)
-        outs.append(weight @ v[:, kh])
-    return mm(torch.stack(outs, 1).reshape(T, H * dv), w[p + "o"].T)
+    o = sigmoid_core(q, k, v, m["scale"], m.get("mask"), w[p + "pb"])
+    return mm(o.reshape(T, H * dv), w[p + "o"].T)
 
 
 def side_by_side(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> torch.Tensor:
     left = sigmoid_attention(h, w, p + "left.", m["left"], eps)
     right = retention(h, w, p + "right.", m["right"], eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
 def relu_squared_ff(h: torch.Tensor, w: dict, p: str) -> torch.Tensor:
