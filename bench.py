@@ -14,7 +14,7 @@ Weights are random (written as a model folder by the library's random-weights mo
 from there), token ids are seeded uniform-random: there is no network for checkpoints or data.
 The library runs on one GPU; with --gpus N > 1 a line says so and the exit code is 2.
 
-``--compare pofadra`` does the same for the Pofadra decoder.  ``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
+``--compare pofadra`` and ``--compare rezulorn`` do the same for the Pofadra and the Rezulorn decoders.  ``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
 at equal layer sizes (prefill and decode throughput of both, and the new design's kernels one by one against their rooflines).
 """
 
@@ -1011,6 +1011,236 @@ def run_compare_pofadra(args) -> dict:
             "results": results}
 
 
+# --compare rezulorn: the Rezulorn decoder (decayed linear attention, scored attention with a distance term and a window
+# that keeps the first tokens, pairs of sigmoid-weighted attention and retention; squared-relu feed-forwards) beside the
+# dense transformer at equal width, and its kernels one by one beside the like kernels of the models that were here.
+def _rezulorn_config(width, layers, heads, kv_heads, dim, window, keep, l_heads, l_dim, l_vdim, p_heads, p_kv, r_heads, r_dim, rot, ff,
+                     vocab):
+    def decays(n):
+        return [1.0 - 2.0 ** (-3 - 6 * i / max(1, n - 1)) for i in range(n)]
+
+    lightning = {"heads": l_heads, "dim": l_dim, "vdim": l_vdim, "decay": decays(l_heads)}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "mask": {"size": window, "keep_first": keep}}
+    pair = {"left": {"heads": p_heads, "kv_heads": p_kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "rot": {"base": 500000.0, "dims": rot, "scaling": {"factor": 2.0}}},
+            "right": {"heads": r_heads, "dim": r_dim, "vdim": r_dim, "decay": decays(r_heads), "rot": {"base": 10000.0, "dims": rot // 2}},
+            "left_scale": 0.6, "right_scale": 0.9}
+    kinds = {"parallel": pair, "lightning": lightning, "attention": attention}
+    order = ["parallel", "lightning", "attention", "parallel"]
+    stack = [{"type": order[i % 4], "mixer": kinds[order[i % 4]], "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]
+    return {"architecture": "Rezulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "residual_mult": 0.5,
+            "logit_scale": 0.25, "layers": stack, "initializer_range": 0.02, "max_position_embeddings": 4096}
+
+
+REZULORN_SIZES = {
+    # name: (Rezulorn sizes, transformer sizes); 8 layers each, vocabulary 32,768; the two matrices of a squared-relu
+    # feed-forward hold about what the three of the transformer's gated one hold
+    "width1024": (dict(width=1024, layers=8, heads=16, kv_heads=4, dim=64, window=1024, keep=64, l_heads=8, l_dim=128, l_vdim=128,
+                       p_heads=8, p_kv=2, r_heads=8, r_dim=64, rot=64, ff=4096, vocab=32768),
+                  dict(hidden=1024, layers=8, heads=16, kv_heads=8, head_dim=128, ff=3072, vocab=32768)),
+    "width2048": (dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, window=1024, keep=64, l_heads=16, l_dim=128, l_vdim=128,
+                       p_heads=8, p_kv=2, r_heads=8, r_dim=128, rot=64, ff=8192, vocab=32768),
+                  dict(hidden=2048, layers=8, heads=16, kv_heads=8, head_dim=128, ff=6144, vocab=32768)),
+}
+
+
+def _rezulorn_prefill_flops(d: dict, tokens: int) -> float:
+    w, dim = d["width"], d["dim"]
+    windowed = sum(min(t + 1, d["window"] + d["keep"]) for t in range(tokens))
+    causal = tokens * (tokens + 1) // 2
+    ff = 4 * w * d["ff"]
+    lightning = 2 * w * d["l_heads"] * (2 * d["l_dim"] + 2 * d["l_vdim"]) + 2 * d["l_heads"] * d["l_vdim"] * w + 4 * d["l_heads"] * d["l_dim"] * d["l_vdim"]
+    attention = 2 * w * (d["heads"] + 2 * d["kv_heads"]) * dim + 2 * d["heads"] * dim * w
+    left = 2 * w * (d["p_heads"] + 2 * d["p_kv"]) * dim + 2 * d["p_heads"] * dim * w
+    right = 2 * w * d["r_heads"] * 4 * d["r_dim"] + 2 * d["r_heads"] * d["r_dim"] * w + 4 * d["r_heads"] * d["r_dim"] ** 2
+    total = 0.0
+    for i in range(d["layers"]):
+        kind = ("parallel", "lightning", "attention", "parallel")[i % 4]
+        if kind == "lightning":
+            total += (lightning + ff) * tokens
+        elif kind == "attention":
+            total += (attention + ff) * tokens + 4 * d["heads"] * dim * windowed
+        else:
+            total += (left + right + ff) * tokens + 4 * d["p_heads"] * dim * causal
+    return total + 2 * w * d["vocab"]
+
+def _rezulorn_kernel_table(d: dict, t: dict, peak: dict) -> dict:
+    """The new design's kernels alone and the like kernels of the transformer (attention, norms) and of the delta-rule
+    decoder (the recurrence and the norm behind it), each with its share of its roofline."""
+    import torch
+
+    from gtar_kimik3_public_b200.ops import functional as F
+
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(48 << 20, dtype=torch.float32, device=dev)  # 192 MB: larger than the 126 MB L2
+    hbm, tflops = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+    out = {}
+
+    def record(name, ms, n_bytes, flops=0.0):
+        floor = max(n_bytes / hbm, flops / tflops) * 1e3
+        out[name] = {"us": round(ms * 1e3, 2), "roofline_us": round(floor * 1e3, 2), "frac": round(floor / ms, 4),
+                     "bound": "hbm" if n_bytes / hbm >= flops / tflops else "tensor"}
+
+    w, dim, window, keep = d["width"], d["dim"], d["window"], d["keep"]
+    aq, ak, pq, pk = d["heads"], d["kv_heads"], d["p_heads"], d["p_kv"]
+    H, dk, dv = d["l_heads"], d["l_dim"], d["l_vdim"]
+    bf = torch.bfloat16
+    for label, tokens, n_seqs in (("prefill_2048", 2048, 1), ("decode_b8_ctx2048", 8, 8)):
+        each = tokens // n_seqs
+        inner = 1 if n_seqs == 1 else 20
+        past = 0 if n_seqs == 1 else 2047
+        length = past + each
+        pages_each = -(-length // 64)
+        table = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).view(n_seqs, pages_each)
+        tok_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each)
+        tok_pos = (torch.arange(each, dtype=torch.int32, device=dev) + past).repeat(n_seqs)
+        cu_q = torch.arange(n_seqs + 1, dtype=torch.int32, device=dev) * each
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        kv_len = torch.full((n_seqs,), length, dtype=torch.int32, device=dev)
+        # ---- the stream: layer norm with the pending branch, the convolution over time, the sum of a pair
+        hs = torch.randn(tokens, w, device=dev)
+        branch = torch.randn(tokens, w, device=dev).to(bf)
+        wn = torch.ones(w, device=dev)
+        ms = _event_ms(lambda: F.add_layernorm(hs, branch, wn, 1e-5, torch.float32, delta_scale=0.5), flush=flush, inner=inner)
+        record(f"rezulorn residual add with layer norm, {label}", ms, tokens * w * (4 + 2 + 4 + 4))
+        ms = _event_ms(lambda: F.add_rmsnorm(hs, branch, wn, 1e-6, bf), flush=flush, inner=inner)
+        record(f"transformer residual add with next norm, {label}", ms, tokens * w * (4 + 2 + 4 + 2))
+        normed = torch.randn(tokens, w, device=dev)
+        conv_w, conv_state = torch.randn(4, w, device=dev) * 0.3, torch.zeros(n_seqs, 3, w, device=dev)
+        ms = _event_ms(lambda: F.causal_conv(normed, conv_w, conv_state, tok_pos, tok_seq, cu_q, slots, bf, update_single_token_state=n_seqs > 1),
+                       flush=flush, inner=inner)
+        record(f"rezulorn convolution over time, {label}", ms, tokens * w * (4 + 2) + (n_seqs * 3 * w * 8 if n_seqs > 1 else 0))
+        ms = _event_ms(lambda: F.scaled_sum(branch, 0.6, branch, 0.9), flush=flush, inner=inner)
+        record(f"rezulorn sum of a pair's branches, {label}", ms, tokens * w * (2 + 2 + 4))
+        # ---- the recurrence with a fixed decay, beside the delta rule at the same heads
+        proj = (torch.randn(tokens, H * (2 * dk + 2 * dv), device=dev) * 0.5).to(bf)
+        ms = _event_ms(lambda: F.heads_prepare(proj, 0, H * dk, 2 * H * dk, H, H, dk, dv, tok_pos, tok_seq, slots, silu_qk=True, silu_v=True),
+                       flush=flush, inner=inner)
+        record(f"rezulorn SiLU of q, k, v into 32-bit arrays, {label}", ms, tokens * H * (2 * dk + dv) * (2 + 4))
+        q, k, v = F.heads_prepare(proj, 0, H * dk, 2 * H * dk, H, H, dk, dv, tok_pos, tok_seq, slots, silu_qk=True, silu_v=True)
+        q *= dk ** -0.5
+        decay = torch.linspace(0.9, 0.999, H, device=dev)
+        state = torch.zeros(n_seqs, H, dk, dv, device=dev)
+        ms = _event_ms(lambda: F.decay_scan(q, k, v, decay, state, cu_q, slots, n_seqs), flush=flush, inner=inner)
+        scan_bytes = 4 * (tokens * H * (2 * dk + 2 * dv) + 2 * n_seqs * H * dk * dv)
+        record(f"rezulorn recurrence with a fixed decay, {label}", ms, scan_bytes)
+        g, beta = torch.exp(-torch.rand(tokens, H, dk, device=dev) * 0.1), torch.rand(tokens, H, device=dev)
+        kn = torch.nn.functional.normalize(k, dim=-1)
+        ms = _event_ms(lambda: F.delta_scan(q, kn, v, g, beta, state, cu_q, slots, n_seqs), flush=flush, inner=inner)
+        record(f"delta-rule decoder recurrence at the same heads, {label}", ms, scan_bytes + 4 * tokens * H * (dk + 1))
+        o = torch.randn(tokens, H * dv, device=dev)
+        norm_w = torch.ones(H * dv, device=dev)
+        ms = _event_ms(lambda: F.group_norm_gate(o, H * dv, norm_w, proj, 2 * H * dk + H * dv, 1e-5, bf, "sigmoid"), flush=flush, inner=inner)
+        record(f"rezulorn norm over all heads with sigmoid gate, {label}", ms, tokens * H * dv * (4 + 2 + 2))
+        ms = _event_ms(lambda: F.group_norm_gate(o, dv, None, proj, 2 * H * dk + H * dv, 1e-5, bf, "silu"), flush=flush, inner=inner)
+        record(f"rezulorn unit heads with SiLU gate, {label}", ms, tokens * H * dv * (4 + 2 + 2))
+        head_w = torch.ones(dv, device=dev)
+        gate32 = torch.randn(tokens, H * dv, device=dev)
+        ms = _event_ms(lambda: F.head_norm_gate(o.view(tokens, H, dv), head_w, gate32, 0, 1e-6, bf), flush=flush, inner=inner)
+        record(f"delta-rule decoder head norm and gate, {label}", ms, tokens * H * dv * (4 + 4 + 2))
+        # ---- scored attention beside the transformer's
+        def pages(n_heads, size):
+            return F.PagedKV(torch.randn(n_seqs * pages_each, n_heads, 64, size, device=dev).to(bf) * 0.1,
+                             torch.randn(n_seqs * pages_each, n_heads, 64, size, device=dev).to(bf) * 0.1, table, F.DecodeWork(dev))
+
+        kv = pages(ak, dim)
+        wide = torch.randn(tokens, (aq + 2 * ak) * dim, device=dev).to(bf)
+        ms = _event_ms(lambda: F.heads_prepare(wide, 0, aq * dim, (aq + ak) * dim, aq, ak, dim, dim, tok_pos, tok_seq, slots, kv=kv,
+                                               max_position=length - 1), flush=flush, inner=inner)
+        record(f"rezulorn cache write (no rotation), {label}", ms, tokens * 2 * ((aq + 2 * ak) * dim + aq * dim + 2 * ak * dim))
+        angle = torch.arange(length, dtype=torch.float32, device=dev)[:, None] * torch.rand(d["rot"] // 2, device=dev)[None, :]
+        cos, sin = angle.cos().contiguous(), angle.sin().contiguous()
+        kvp = pages(pk, dim)
+        widep = torch.randn(tokens, (pq + 2 * pk) * dim, device=dev).to(bf)
+        ms = _event_ms(lambda: F.heads_prepare(widep, 0, pq * dim, (pq + pk) * dim, pq, pk, dim, dim, tok_pos, tok_seq, slots, rot=d["rot"],
+                                               cos=cos, sin=sin, unit_eps=1e-5, kv=kvp, max_position=length - 1), flush=flush, inner=inner)
+        record(f"rezulorn rotation, unit q and k, cache write, {label}", ms, tokens * 2 * ((pq + 2 * pk) * dim + pq * dim + 2 * pk * dim))
+        qa = torch.randn(tokens, aq, dim, device=dev).to(bf)
+        r1, r2 = torch.full((aq,), 0.3, device=dev), torch.full((aq,), 0.5, device=dev)
+        seen = sum(min(p + 1, window) + min(keep, max(0, p + 1 - window)) for p in range(past, length)) * n_seqs
+        parts = F.scored_attention_parts(n_seqs, aq, ak, each, -(-(window + keep) // 64) + 2, F.sm_count(dev))
+        ms = _event_ms(lambda: F.attention_scored(qa, kv, cu_q, kv_len, slots, each, dim ** -0.5, window, keep, r1, r2, None, "softmax", parts),
+                       flush=flush, inner=inner)
+        attn_bytes = 2 * (2 * tokens * aq * dim + 2 * n_seqs * min(length, window + keep + each) * ak * dim)
+        record(f"rezulorn attention: distance term, window {window} keeping {keep}, softmax, {label}", ms, attn_bytes, 4 * aq * dim * seen)
+        ms = _event_ms(lambda: F.attention_scored_exact(qa, kv, tok_pos, tok_seq, slots, dim ** -0.5, window, keep, r1, r2, None, "softmax"),
+                       flush=flush, inner=inner, repeats=3)
+        record(f"rezulorn attention, the same on the exact kernel (what 32-bit runs use), {label}", ms, attn_bytes, 4 * aq * dim * seen)
+        qp = torch.randn(tokens, pq, dim, device=dev).to(bf)
+        pb = torch.full((pq,), -4.0, device=dev)
+        causal = sum(p + 1 for p in range(past, length)) * n_seqs
+        parts = F.scored_attention_parts(n_seqs, pq, pk, each, pages_each, F.sm_count(dev))
+        ms = _event_ms(lambda: F.attention_scored(qp, kvp, cu_q, kv_len, slots, each, dim ** -0.5, 0, 0, None, None, pb, "sigmoid", parts),
+                       flush=flush, inner=inner)
+        record(f"rezulorn attention: causal, sigmoid weights, {label}", ms, 2 * (2 * tokens * pq * dim + 2 * n_seqs * length * pk * dim),
+               4 * pq * dim * causal)
+        hq, hk, hd = t["heads"], t["kv_heads"], t["head_dim"]
+        kvt = pages(hk, hd)
+        qt = torch.randn(tokens, hq, hd, device=dev).to(bf)
+        if n_seqs == 1:
+            ms = _event_ms(lambda: F.attention_prefill(qt, kvt, cu_q, kv_len, slots, each, hd ** -0.5, 0), flush=flush, inner=inner)
+            record(f"transformer attention, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * length * hk * hd), 4 * hq * hd * causal)
+            ms = _event_ms(lambda: F.attention_prefill(qt, kvt, cu_q, kv_len, slots, each, hd ** -0.5, 0, tensor_cores="mma"), flush=flush, inner=inner)
+            record(f"transformer attention on the warp-level kernel, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * length * hk * hd),
+                   4 * hq * hd * causal)
+            ms = _event_ms(lambda: F.attention_prefill(qt, kvt, cu_q, kv_len, slots, each, hd ** -0.5, window, tensor_cores="mma"), flush=flush,
+                           inner=inner)
+            record(f"transformer attention on the warp-level kernel with window {window}, {label}", ms,
+                   2 * (2 * tokens * hq * hd + 2 * length * hk * hd), 4 * hq * hd * sum(min(p + 1, window) for p in range(length)))
+        else:
+            sp = F.decode_splits(n_seqs, hk, length, 64, F.sm_count(dev), F.decode_cluster_places(hd, F.sm_count(dev)))
+            ms = _event_ms(lambda: F.attention_decode(qt, kvt, kv_len, slots, hd ** -0.5, 0, sp), flush=flush, inner=inner)
+            record(f"transformer attention, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * n_seqs * length * hk * hd), 4 * hq * hd * tokens * length)
+            sp = F.decode_splits(n_seqs, hk, window, 64, F.sm_count(dev), F.decode_cluster_places(hd, F.sm_count(dev)))
+            ms = _event_ms(lambda: F.attention_decode(qt, kvt, kv_len, slots, hd ** -0.5, window, sp), flush=flush, inner=inner)
+            record(f"transformer attention with window {window}, {label}", ms, 2 * (2 * tokens * hq * hd + 2 * n_seqs * window * hk * hd),
+                   4 * hq * hd * tokens * window)
+        qkv = torch.randn(tokens, (hq + 2 * hk) * hd, device=dev).to(bf)
+        anglet = torch.arange(length, dtype=torch.float32, device=dev)[:, None] * torch.rand(hd // 2, device=dev)[None, :]
+        cost, sint = anglet.cos().contiguous(), anglet.sin().contiguous()
+        ones = torch.ones(hd, device=dev)
+        ms = _event_ms(lambda: F.qk_norm_rope_write(qkv, hq, hk, hd, ones, ones, 1e-6, cost, sint, tok_pos, tok_seq, slots, kvt, length - 1),
+                       flush=flush, inner=inner)
+        record(f"transformer q/k norm, rotation and cache write, {label}", ms, tokens * 2 * ((hq + 2 * hk) * hd + hq * hd + 2 * hk * hd))
+    return out
+
+
+def run_compare_rezulorn(args) -> dict:
+    import gc
+
+    import torch
+
+    from gtar_kimik3_public_b200.ops.library import require_device
+
+    require_device(torch.device("cuda:0"))
+    peak, peak_source = peaks()
+    results = {}
+    for name, (d, t) in REZULORN_SIZES.items():
+        entry = {}
+        for arch, raw, flops in (("rezulorn", _rezulorn_config(**d), _rezulorn_prefill_flops(d, PREFILL_TOKENS)),
+                                 ("transformer", _transformer_config(**t), _transformer_prefill_flops(t, PREFILL_TOKENS))):
+            model = _device_model(raw)
+            ms = _time_prefill_ms(model, PREFILL_TOKENS)
+            decode = time_decode(model, args.batch, min(args.steps, 64), args.warmup)
+            entry[arch] = {
+                "weight_bytes_per_step": model.weight_bytes_per_step(),
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / (ms / 1e3), 1), "prefill_ms": round(ms, 3),
+                "prefill_frac_of_bf16_peak": round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                "decode_frac_of_hbm_peak": round(decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4),
+                "decode_launches_per_step": decode["launches"] // max(1, min(args.steps, 64)),
+            }
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        entry["kernels"] = _rezulorn_kernel_table(d, t, peak)
+        results[name] = {"sizes": {"rezulorn": d, "transformer": t}, **entry}
+    return {"compare": "rezulorn beside transformer at equal width", "batch": args.batch, "prompt_tokens": PROMPT_LEN,
+            "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16", "data": "synthetic: random token ids, random weights drawn on the device",
+            "peaks": dict(peak, source=peak_source), "l2": "single kernels: a 192 MB buffer is written between the timed calls of the 2,048-token cases; the 8-token cases are 20 calls back to back from a CUDA graph",
+            "results": results}
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -1020,13 +1250,14 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--no-large", action="store_true", help="leave out the points at the 4B and 8B layer sizes")
-    parser.add_argument("--compare", default=None, choices=["dasusun", "pofadra"],
+    parser.add_argument("--compare", default=None, choices=["dasusun", "pofadra", "rezulorn"],
                         help="instead of the default workload: this architecture beside the transformer at equal layer sizes")
     args = parser.parse_args()
     if args.compare:
         if args.warmup < 3:
             args.warmup = 3
-        print(json.dumps(run_compare_pofadra(args) if args.compare == "pofadra" else run_compare(args)))
+        runner = {"pofadra": run_compare_pofadra, "rezulorn": run_compare_rezulorn, "dasusun": run_compare}[args.compare]
+        print(json.dumps(runner(args)))
         return 0
     if args.impl == "reference":
         if args.warmup < 3:
