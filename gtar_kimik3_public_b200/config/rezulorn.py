@@ -63,8 +63,6 @@ def _check_softmax_kind(where: str, m: Any) -> None:
     _number(where + ".scale", m["scale"])
     if m["heads"] % m["kv_heads"]:
         raise ConfigError(f"{_NAME}: {where}.heads ({m['heads']}) must be a multiple of kv_heads ({m['kv_heads']})")
-    if m["dim"] % 8:
-        raise ConfigError(f"{_NAME}: {where}.dim ({m['dim']}) must be a multiple of 8")
     _check_rot(where + ".rot", m.get("rot"), m["dim"])
     if m.get("mask") is not None:
         mask = _need(where + ".mask", m["mask"], ("size",), ("keep_first",))
@@ -78,8 +76,8 @@ def _check_decay_kind(where: str, m: Any) -> None:
     _need(where, m, ("heads", "dim", "vdim", "decay"), ("rot",))
     for key in ("heads", "dim", "vdim"):
         _int(f"{where}.{key}", m[key])
-    if m["dim"] % 4 or m["dim"] > 256:
-        raise ConfigError(f"{_NAME}: {where}.dim ({m['dim']}) must be a multiple of 4, at most 256")
+    if m["dim"] > 256:
+        raise ConfigError(f"{_NAME}: {where}.dim ({m['dim']}) must be at most 256 (a state's rows are held by eight lanes)")
     decay = m["decay"]
     if not isinstance(decay, list) or len(decay) != m["heads"]:
         raise ConfigError(f"{_NAME}: {where}.decay must list one number per head ({m['heads']})")

@@ -26,6 +26,10 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* _
 template <>
 __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, const float* __restrict__ k, int d) {
     float acc = 0.f;
+    if (d & 3) {  // rows that do not start on 16 bytes: one entry at a time
+        for (int i = 0; i < d; ++i) acc = fmaf(q[i], k[i], acc);
+        return acc;
+    }
     for (int i = 0; i < d; i += 4) {
         const float4 kv = *reinterpret_cast<const float4*>(k + i);
         acc = fmaf(q[i], kv.x, acc);
@@ -39,6 +43,10 @@ __device__ __forceinline__ float dot_row<float>(const float* __restrict__ q, con
 template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int d) {
     float acc = 0.f;
+    if (d & 7) {  // rows that do not start on 16 bytes: one entry at a time
+        for (int i = 0; i < d; ++i) acc = fmaf(q[i], __bfloat162float(k[i]), acc);
+        return acc;
+    }
     for (int i = 0; i < d; i += 8) {
         const uint4 raw = *reinterpret_cast<const uint4*>(k + i);
         const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -143,8 +151,8 @@ GK_EXPORT int gk_attention_scored_exact(const void* q, const void* k_pages, cons
                                         int weights, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype), "attention_scored: bad dtype %d", dtype);
     GK_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_scored: bad head counts %d/%d", n_q, n_kv);
-    GK_REQUIRE(d > 0 && d % 8 == 0 && dv > 0 && dv <= 32 * MAX_ACC, "attention_scored: keys of %d must be a multiple of 8, values of %d at most %d",
-               d, dv, 32 * MAX_ACC);
+    GK_REQUIRE(d > 0 && dv > 0 && dv <= 32 * MAX_ACC, "attention_scored: keys of %d must be positive, values of %d at most %d", d, dv,
+               32 * MAX_ACC);
     GK_REQUIRE(page_size > 0 && page_size % 32 == 0, "attention_scored: page_size %d must be a multiple of 32", page_size);
     GK_REQUIRE(window >= 0 && keep_first >= 0, "attention_scored: window and kept first keys must be >= 0 (0 = none)");
     GK_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_scored: the distance term needs both of its numbers");

@@ -168,6 +168,15 @@ __global__ void __launch_bounds__(SCAN_LANES * SCAN_MAX_COLS) decay_scan_kernel(
     const int quads = d / 4;
     auto stage = [&](int buf, int first) {
         const int count = min(TB, n - first);
+        if (d & 3) {  // rows that do not start on 16 bytes: one entry a copy
+            for (int i = threadIdx.x; i < count * d; i += n_threads) {
+                const int tt = i / d, c = i - tt * d;
+                const int at = (c / R) * PIECE + c % R;
+                const size_t tok = (size_t)(t0 + first + tt);
+                cp_async4(&sq[buf][tt][at], q + (tok * n_heads + head) * d + c);
+                cp_async4(&sk[buf][tt][at], k + (tok * n_heads + head) * d + c);
+            }
+        } else
         for (int i = threadIdx.x; i < count * quads; i += n_threads) {
             const int tt = i / quads, c4 = (i - tt * quads) * 4;
             const int at = (c4 / R) * PIECE + c4 % R;
@@ -293,7 +302,7 @@ GK_EXPORT int gk_heads_prepare(const void* proj, int dtype, long long ld, int q_
 GK_EXPORT int gk_decay_scan(const float* q, const float* k, const float* v, const float* decay, float* state, float* out,
                             const int* cu_q, const int* slots, int n_seqs, int n_heads, int d, int dv, void* stream) {
     GK_REQUIRE(n_heads > 0 && n_heads <= 65535 && n_seqs >= 0 && n_seqs <= 65535, "decay_scan: bad counts");
-    GK_REQUIRE(d > 0 && d % 4 == 0 && d <= 256, "decay_scan: key size %d must be a multiple of 4, at most 256", d);
+    GK_REQUIRE(d > 0 && d <= 256, "decay_scan: key size %d must be at most 256", d);
     GK_REQUIRE(dv > 0, "decay_scan: bad value size");
     if (n_seqs == 0) return GK_OK;
     static int sms = 0;

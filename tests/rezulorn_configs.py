@@ -105,4 +105,17 @@ REZ_E = {
     ],
 }
 
-REZ_CONFIGS = {"rez_a": REZ_A, "rez_b": REZ_B, "rez_c": REZ_C, "rez_d": REZ_D, "rez_e": REZ_E}
+# Head sizes that are no multiple of 8 or of 4 (rows of keys and states that start on no 16-byte border), a width that is
+# no multiple of 8, five taps, an odd vocabulary.
+REZ_F = {
+    "architecture": "Rezulorn", "vocab": 131, "width": 52, "norm": {"eps": 1e-5}, "canon": {"taps": 5}, "residual_mult": 0.9,
+    "logit_scale": 0.7,
+    "layers": [
+        _layer("attention", _scored(4, 2, 20, 12, 0.22, window=9, keep_first=2), 44),
+        _layer("parallel", _pair(_scored(3, 1, 10, 6, 0.3, rot=_rot(6, 3000.0, 3.0)),
+                                 _decayed(2, 6, 10, [0.9, 0.99], rot=_rot(2, 50.0)), 1.1, 0.9), 36),
+        _layer("lightning", _decayed(3, 10, 6, [0.8, 0.95, 0.999]), None),
+    ],
+}
+
+REZ_CONFIGS = {"rez_a": REZ_A, "rez_b": REZ_B, "rez_c": REZ_C, "rez_d": REZ_D, "rez_e": REZ_E, "rez_f": REZ_F}

@@ -13,7 +13,7 @@ from tests.rezulorn_helpers import rez_check, rez_engine, rez_folder, rez_plain_
 
 pytestmark = pytest.mark.gpu
 
-TAGS = ("rez_a", "rez_b", "rez_c", "rez_d", "rez_e")
+TAGS = ("rez_a", "rez_b", "rez_c", "rez_d", "rez_e", "rez_f")
 CASES = [(tag, dtype) for tag in TAGS for dtype in ("float32", "bfloat16")]
 LENGTHS = [1, 2, 3, 17, 64, 65, 90, 150]
 
