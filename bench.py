@@ -1124,7 +1124,11 @@ def _rezulorn_kernel_table(d: dict, t: dict, peak: dict) -> dict:
         state = torch.zeros(n_seqs, H, dk, dv, device=dev)
         ms = _event_ms(lambda: F.decay_scan(q, k, v, decay, state, cu_q, slots, n_seqs), flush=flush, inner=inner)
         scan_bytes = 4 * (tokens * H * (2 * dk + 2 * dv) + 2 * n_seqs * H * dk * dv)
-        record(f"rezulorn recurrence with a fixed decay, {label}", ms, scan_bytes)
+        record(f"rezulorn recurrence with a fixed decay, token by token, {label}", ms, scan_bytes)
+        if tokens // n_seqs >= 64:
+            ms = _event_ms(lambda: F.decay_scan_chunked(q, k, v, decay, state, cu_q, slots, n_seqs, tokens // n_seqs), flush=flush, inner=inner)
+            chunk_flops = 2.0 * tokens * H * (2 * dk * dv + 64 * dk // 2 + 64 * dv // 2)
+            record(f"rezulorn recurrence with a fixed decay, in chunks of 64 (32-bit pipe: {chunk_flops / 1e9:.2f} GFLOP), {label}", ms, scan_bytes)
         g, beta = torch.exp(-torch.rand(tokens, H, dk, device=dev) * 0.1), torch.rand(tokens, H, device=dev)
         kn = torch.nn.functional.normalize(k, dim=-1)
         ms = _event_ms(lambda: F.delta_scan(q, kn, v, g, beta, state, cu_q, slots, n_seqs), flush=flush, inner=inner)

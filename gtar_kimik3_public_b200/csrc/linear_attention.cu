@@ -261,6 +261,31 @@ __global__ void __launch_bounds__(256) group_norm_gate_kernel(const float* __res
     }
 }
 
+// The same for wide groups, a block per row: a warp alone would walk a row of a thousand entries in 32 dependent rounds.
+template <typename T, typename TG>
+__global__ void __launch_bounds__(256) group_norm_gate_wide_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                                   const TG* __restrict__ gate, long long ld_gate, T* __restrict__ out,
+                                                                   int n_groups, int size, float eps, int gate_kind) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long row = blockIdx.x;
+    const long long t = row / n_groups;
+    const int g = (int)(row - t * n_groups);
+    const float* xr = x + (size_t)row * size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += 256) ss = fmaf(xr[i], xr[i], ss);
+    ss = block_sum(ss, scratch);
+    const float r = 1.f / sqrtf(ss / (float)size + eps);
+    const TG* gt = gate + (size_t)t * ld_gate + (size_t)g * size;
+    for (int i = threadIdx.x; i < size; i += 256) {
+        const float z = to_float(gt[i]);
+        float y = xr[i] * r;
+        if (weight != nullptr) y *= weight[i];
+        out[(size_t)row * size + i] = from_float<T>(y * (gate_kind == 0 ? sigmoid_f(z) : silu_f(z)));
+    }
+}
+
 }  // namespace
 
 GK_EXPORT int gk_heads_prepare(const void* proj, int dtype, long long ld, int q_at, int k_at, int v_at, int n_q, int n_k, int d,
@@ -337,10 +362,15 @@ GK_EXPORT int gk_group_norm_gate(const float* x, const float* weight, const void
     const long long blocks = (rows + 7) / 8;
     GK_REQUIRE(blocks < 2147483647LL, "group_norm_gate: too many rows");
     cudaStream_t s = (cudaStream_t)stream;
+    const bool wide = size >= 512 && rows < 2147483647LL;  // by the group's size alone: a row's sums never depend on the step
     GK_DISPATCH_DTYPE(out_dtype, T, {
         GK_DISPATCH_DTYPE(gate_dtype, TG, {
-            gk_launch(group_norm_gate_kernel<T, TG>, dim3((unsigned)blocks), dim3(256), 0, s, x, weight, (const TG*)gate, ld_gate,
-                      (T*)out, rows, n_groups, size, eps, gate_kind);
+            if (wide)
+                gk_launch(group_norm_gate_wide_kernel<T, TG>, dim3((unsigned)rows), dim3(256), 0, s, x, weight, (const TG*)gate, ld_gate,
+                          (T*)out, n_groups, size, eps, gate_kind);
+            else
+                gk_launch(group_norm_gate_kernel<T, TG>, dim3((unsigned)blocks), dim3(256), 0, s, x, weight, (const TG*)gate, ld_gate,
+                          (T*)out, rows, n_groups, size, eps, gate_kind);
         })
     })
     GK_CHECK_LAUNCH("group_norm_gate");

@@ -1601,6 +1601,40 @@ def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.T
     return out
 
 
+DECAY_CHUNK = 64                 # tokens a chunk of decay_scan_chunked
+DECAY_WORKSPACE_FLOATS = 1 << 26  # at most this many 32-bit numbers of chunk states in flight (256 MB)
+
+
+def decay_scan_chunked_fits(d: int, dv: int) -> bool:
+    """Whether :func:`decay_scan_chunked` takes heads of these sizes: rows of 16-byte vectors, and the transposed q and k
+    tiles, a tile of values and a tile of weights within 200 KB of shared memory (the kernel's own rule)."""
+    return d > 0 and dv > 0 and d % 4 == 0 and dv % 4 == 0 and (2 * d * 68 + 64 * 64 + 64 * 68 + 68) * 4 <= 200 * 1024
+
+
+def decay_scan_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor,
+                       slots: torch.Tensor, n_seqs: int, max_q_len: int) -> torch.Tensor:
+    """:func:`decay_scan` for steps of many tokens: the tokens of every sequence are cut into chunks of 64 whose inner
+    work is matrix products that run side by side, with one short pass over the chunks in sequence between them.  32-bit
+    throughout; the sums have another order than token by token, so the two agree within rounding.  ``max_q_len`` bounds
+    the sequences' token counts in this step."""
+    require_device(q.device)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check(t, name, torch.float32, 3)
+    _check(decay, "decay", torch.float32, 1)
+    _check(state, "state", torch.float32, 4)
+    T, n_heads, d = q.shape
+    dv = v.shape[2]
+    if k.shape != q.shape or tuple(v.shape[:2]) != (T, n_heads) or tuple(state.shape[1:]) != (n_heads, d, dv) or decay.shape[0] != n_heads:
+        raise KernelError("decay_scan_chunked: the state, the decays or the inputs have other sizes than the heads")
+    out = torch.empty((T, n_heads, dv), dtype=torch.float32, device=q.device)
+    chunks = max(1, -(-int(max_q_len) // DECAY_CHUNK))
+    wave = max(1, min(chunks, DECAY_WORKSPACE_FLOATS // max(1, n_seqs * n_heads * d * dv)))
+    ws = torch.empty((max(1, n_seqs) * wave * n_heads * d * dv,), dtype=torch.float32, device=q.device)
+    call("gk_decay_scan_chunked", ptr(q), ptr(k), ptr(v), ptr(decay), ptr(state), ptr(out), ptr(ws), ptr(cu_q), ptr(slots), int(n_seqs),
+         n_heads, d, dv, int(max_q_len), wave, stream_ptr())
+    return out
+
+
 def group_norm_gate(x: torch.Tensor, group: int, weight: torch.Tensor | None, gate: torch.Tensor, gate_at: int, eps: float,
                     out_dtype: torch.dtype, gate_kind: str = "sigmoid") -> torch.Tensor:
     """Rows of ``x [T, width]`` (32-bit) cut into groups of ``group`` entries; every group divided by its root mean square

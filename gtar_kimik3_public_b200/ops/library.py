@@ -85,6 +85,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_scale": [P, L, F, P],
     "gk_heads_prepare": [P, I, L, I, I, I, I, I, I, I, I, I, P, P, F, F, P, P, P, P, I, P, P, P, P, P, I, I, I, I, P],
     "gk_decay_scan": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "gk_decay_scan_chunked": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "gk_group_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, I, P],
     "gk_attention_scored_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, I, P],
     "gk_attention_scored_bf16": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, P],

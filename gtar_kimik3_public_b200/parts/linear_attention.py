@@ -20,7 +20,9 @@ between the recurrence and the output projection, is chosen by the builder:
 Everything from the activations to the gate is 32-bit.  What a sequence keeps between steps: the states of all heads.
 
 A step's kernels: the packed projection q | k | v | gate; one kernel for activation, rotation and scale; the recurrence;
-norm and gate; the output projection.  Prompts, portions of prompts and single tokens take the same path.
+norm and gate; the output projection.  The recurrence runs token by token where a step brings few tokens a sequence
+and in 32-bit runs (there a token's sums have the same order however a prompt is cut), and in chunks of 64 tokens whose
+inner work is matrix products in bfloat16 runs with many tokens (the same numbers within 32-bit rounding).
 """
 
 from __future__ import annotations
@@ -37,6 +39,7 @@ _NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
 
 class DecayLinearAttention(Mixer):
     graph_safe = True  # kernels only; starts and slots are read from device memory
+    chunked_from = 48  # steps whose longest sequence brings this many tokens take the chunked kernels (bfloat16 runs)
 
     def __init__(self, hidden_size: int, n_heads: int, key_dim: int, value_dim: int, decay, norm_eps: float,
                  activation: str | None = None, position: PositionEncoding | None = None, k_scale: float = 1.0,
@@ -94,7 +97,10 @@ class DecayLinearAttention(Mixer):
         proj = linear(x, self.w_in)
         q, k, v = F.heads_prepare(proj, 0, H * d, 2 * H * d, H, H, d, dv, ctx.tok_pos, ctx.tok_seq, ctx.slots, silu_qk=silu,
                                   silu_v=silu, rot=self.rot, cos=cos, sin=sin, k_scale=self.k_scale, max_position=ctx.max_position)
-        o = F.decay_scan(q, k, v, self.decay, cache, ctx.cu_q, ctx.slots, ctx.n_seqs)
+        if ctx.dtype == torch.bfloat16 and ctx.max_q_len >= self.chunked_from and F.decay_scan_chunked_fits(d, dv):
+            o = F.decay_scan_chunked(q, k, v, self.decay, cache, ctx.cu_q, ctx.slots, ctx.n_seqs, ctx.max_q_len)
+        else:  # few tokens a sequence, and 32-bit runs (whose numbers do not depend on how a prompt is cut)
+            o = F.decay_scan(q, k, v, self.decay, cache, ctx.cu_q, ctx.slots, ctx.n_seqs)
         group = H * dv if self.read_norm == "all" else dv
         y = F.group_norm_gate(o.view(ctx.n_tokens, H * dv), group, self.norm_w, proj, 2 * H * d + H * dv, self.norm_eps, ctx.dtype,
                               self.gate)

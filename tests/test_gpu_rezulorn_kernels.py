@@ -249,9 +249,65 @@ def test_decay_scan_remembers_a_far_token():
     assert (out.double().cpu() - want).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("H,d,dv,lengths", [(3, 24, 40, [90]), (2, 64, 128, [200, 64, 1]), (1, 132, 20, [63, 65, 128]),
+                                            (5, 8, 8, [150, 2]), (2, 4, 12, [129]), (1, 256, 36, [70]), (2, 128, 68, [300, 17])])
+def test_decay_scan_in_chunks_against_token_by_token(H, d, dv, lengths):
+    """The chunked kernels on batches of unequal sequences that go on from kept states, with chunk borders inside, at and
+    one off the ends, against the recurrence in float64 and against the token-by-token kernel; decays of 1 and 0 too."""
+    gen = torch.Generator(device=DEV).manual_seed(H * d + dv)
+    T, n = sum(lengths), len(lengths)
+    q, k = (torch.randn(T, H, d, generator=gen, device=DEV) for _ in range(2))
+    v = torch.randn(T, H, dv, generator=gen, device=DEV)
+    decay = torch.tensor(([1.0, 0.0, 0.9, 0.999, 0.5] * 2)[:H], device=DEV)
+    begin = torch.randn(n + 2, H, d, dv, generator=gen, device=DEV)
+    slots = list(range(n, 0, -1))
+    _, _, cu = _layout(lengths)
+    assert F().decay_scan_chunked_fits(d, dv)
+    for wave_floats in (1 << 26, 1):  # all chunks in one wave, and one chunk a wave
+        state = begin.clone()
+        before = F().DECAY_WORKSPACE_FLOATS
+        F().DECAY_WORKSPACE_FLOATS = wave_floats
+        try:
+            got = F().decay_scan_chunked(q, k, v, decay, state, cu, _i32(slots), n, max(lengths))
+        finally:
+            F().DECAY_WORKSPACE_FLOATS = before
+        stepped_state = begin.clone()
+        stepped = F().decay_scan(q, k, v, decay, stepped_state, cu, _i32(slots), n)
+        at = 0
+        for length, slot in zip(lengths, slots):
+            S = begin[slot].double().cpu()
+            want = torch.empty(length, H, dv, dtype=torch.float64)
+            for t in range(length):
+                S = decay.double().cpu()[:, None, None] * S + torch.einsum("hd,he->hde", k[at + t].double().cpu(), v[at + t].double().cpu())
+                want[t] = torch.einsum("hde,hd->he", S, q[at + t].double().cpu())
+            scale = max(1.0, want.abs().max().item())
+            assert (got[at:at + length].double().cpu() - want).abs().max().item() < 2e-5 * scale, f"read-outs, wave {wave_floats}"
+            assert (state[slot].double().cpu() - S).abs().max().item() < 2e-5 * max(1.0, S.abs().max().item()), "state behind the step"
+            at += length
+        assert (got - stepped).abs().max().item() < 4e-5 * max(1.0, stepped.abs().max().item())
+        assert torch.equal(state[[0, n + 1]], begin[[0, n + 1]]), "another slot's state was written"
+
+
+def test_decay_scan_in_chunks_remembers_a_far_token():
+    """One large key-value pair at the first token, read by the last token 600 tokens later, through nine chunk borders."""
+    H, d, dv, T = 2, 16, 8, 601
+    gen = torch.Generator(device=DEV).manual_seed(2)
+    q, k = (torch.randn(T, H, d, generator=gen, device=DEV) * 0.01 for _ in range(2))
+    v = torch.randn(T, H, dv, generator=gen, device=DEV) * 0.01
+    k[0, :, 3], v[0, :, 5], q[T - 1, :, 3] = 10.0, 10.0, 10.0
+    decay = torch.tensor([0.999, 0.9], device=DEV)
+    state = torch.zeros(1, H, d, dv, device=DEV)
+    _, _, cu = _layout([T])
+    out = F().decay_scan_chunked(q, k, v, decay, state, cu, _i32([0]), 1, T)
+    assert abs(out[T - 1, 0, 5].item() - 1000.0 * 0.999 ** 600) < 1.0
+    assert abs(out[T - 1, 1, 5].item()) < 0.1
+    assert (out.double().cpu() - _scan_whole(q, k, v, decay)).abs().max().item() < 1e-3
+
+
 # ------------------------------------------------------------------ norm and gate behind the recurrence
 @pytest.mark.parametrize("H,dv,whole,gate_kind,out_dtype", [(3, 40, True, "sigmoid", torch.float32), (2, 24, False, "silu", torch.bfloat16),
-                                                            (5, 8, False, "silu", torch.float32), (1, 260, True, "sigmoid", torch.bfloat16)])
+                                                            (5, 8, False, "silu", torch.float32), (1, 260, True, "sigmoid", torch.bfloat16),
+                                                            (4, 160, True, "sigmoid", torch.bfloat16), (2, 516, False, "silu", torch.float32)])
 def test_group_norm_gate(H, dv, whole, gate_kind, out_dtype):
     T, width = 19, H * dv
     gen = torch.Generator(device=DEV).manual_seed(dv)
