@@ -9,7 +9,7 @@
 // Every power of g has a non-negative exponent, so nothing grows: decays of 0 and of 1 are as good as any.  Three
 // kernels a wave of chunks: `local` (a block per chunk, head and 64 value columns), `carry` (an element of the state
 // per thread, the wave's chunks in sequence; it leaves S0 of every chunk where L was), `read` (a block per chunk, head
-// and 64 value columns).  All arithmetic is 32-bit on the FP32 pipe: products of 4 x 4 register tiles whose operands
+// and 64 value columns; S0's columns come into shared memory where the keys were, once the weights are formed).  All arithmetic is 32-bit on the FP32 pipe: products of 4 x 4 register tiles whose operands
 // come from shared memory as 16-byte vectors.  A token's sums have another order than in the token-by-token kernel:
 // the two agree within rounding, not bit by bit.
 
@@ -104,13 +104,22 @@ __global__ void __launch_bounds__(THREADS) decay_chunk_carry_kernel(
     float4* w = reinterpret_cast<float4*>(ws + ((size_t)seq * wave * n_heads + head) * (size_t)size4 * 4) + e;
     const size_t step = (size_t)n_heads * size4;
     float4 s = *st;
-#pragma unroll 4
-    for (int c = 0; c < here; ++c, w += step) {
-        const int n = min(CHUNK, len - (chunk0 + c) * CHUNK);
-        const float gn = n == CHUNK ? powf(g, (float)CHUNK) : powf(g, (float)n);
-        const float4 add = *w;
-        *w = s;
-        s.x = fmaf(gn, s.x, add.x), s.y = fmaf(gn, s.y, add.y), s.z = fmaf(gn, s.z, add.z), s.w = fmaf(gn, s.w, add.w);
+    const float g_full = powf(g, (float)CHUNK);
+    constexpr int AHEAD = 8;  // loads in flight: the chain itself is one multiply-add a chunk
+    for (int c0 = 0; c0 < here; c0 += AHEAD) {
+        float4 add[AHEAD];
+#pragma unroll
+        for (int a = 0; a < AHEAD; ++a)
+            if (c0 + a < here) add[a] = __ldcg(w + (size_t)a * step);
+#pragma unroll
+        for (int a = 0; a < AHEAD; ++a) {
+            if (c0 + a >= here) break;
+            const int n = min(CHUNK, len - (chunk0 + c0 + a) * CHUNK);
+            const float gn = n == CHUNK ? g_full : powf(g, (float)n);
+            __stcg(w + (size_t)a * step, s);
+            s.x = fmaf(gn, s.x, add[a].x), s.y = fmaf(gn, s.y, add[a].y), s.z = fmaf(gn, s.z, add[a].z), s.w = fmaf(gn, s.w, add[a].w);
+        }
+        w += (size_t)AHEAD * step;
     }
     *st = s;
 }
@@ -179,14 +188,25 @@ __global__ void __launch_bounds__(THREADS) decay_chunk_read_kernel(
         }
     }
     __syncthreads();
+    // the keys' tile has done its work: the 64 columns of S0 take its place
+    float* s0 = kt;  // [d][64]
+    {
+        const float* src = ws + (((size_t)seq * wave + in_wave) * n_heads + head) * (size_t)d * dv + c0;
+        for (int i = threadIdx.x; i < d * (CHUNK / 4); i += THREADS) {
+            const int kk = i >> 4, c4 = (i & 15) << 2;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c0 + c4 < dv) x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)kk * dv + c4));
+            *reinterpret_cast<float4*>(s0 + kk * CHUNK + c4) = x;
+        }
+    }
+    __syncthreads();
     const int col = c0 + tx * 4;
     if (col >= dv || i0 >= n) return;  // no barrier below
     float acc[4][4] = {};
-    const float* s0 = ws + (((size_t)seq * wave + in_wave) * n_heads + head) * (size_t)d * dv + col;
 #pragma unroll 4
     for (int kk = 0; kk < d; ++kk) {
         const float4 a = *reinterpret_cast<const float4*>(qt + kk * LDT + i0);
-        const float4 b = __ldg(reinterpret_cast<const float4*>(s0 + (size_t)kk * dv));
+        const float4 b = *reinterpret_cast<const float4*>(s0 + kk * CHUNK + tx * 4);
         const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int p = 0; p < 4; ++p)
