@@ -48,6 +48,72 @@ __global__ void __launch_bounds__(LN_THREADS) add_layernorm_kernel(float* __rest
     for (int i = threadIdx.x; i < hidden; i += LN_THREADS) orow[i] = from_float<TO>((row[i] - mean) * inv * to_float(w[i]));
 }
 
+// Steps in which every sequence brings ONE token: the add, the layer norm and the short convolution over time that
+// reads its result, in one kernel (row t is the token of sequence tok_seq[t]).  With y the normed row,
+//   out = y + sum_j cw[j] * y_(pos - (taps - 1 - j)),
+// where the inputs of earlier positions come from the sequence's state [taps - 1, hidden] (zeros before the sequence's
+// start) and, with `update`, the state is moved on by y.  The norm's and the convolution's sums have the order they have
+// in the kernels that do one of the two, so the numbers are the same: the block has LNC_THREADS threads for the loads
+// of the earlier inputs and for the convolution, a channel or two a thread, and its first LN_THREADS threads alone sum
+// the row, as the norm's own kernel does (the others add zeros, which a sum over the warps does not see).
+constexpr int LNC_THREADS = 1024;
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(LNC_THREADS) add_layernorm_conv_single_kernel(
+    float* __restrict__ h, const TD* __restrict__ delta, float delta_scale, const float* __restrict__ w, const float* __restrict__ cw,
+    float* __restrict__ state, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+    TO* __restrict__ out, int hidden, int taps, float eps, int update) {
+    extern __shared__ float row[];  // hidden floats, then the sequence's taps - 1 earlier inputs [taps - 1, hidden]
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float* hrow = h + (size_t)t * hidden;
+    const bool has_delta = delta != nullptr;
+    const TD* drow = delta + (size_t)t * hidden;
+    const int pos = tok_pos[t];
+    const int kept = taps - 1;
+    float* mine = kept > 0 ? state + (size_t)slots[tok_seq[t]] * kept * hidden : nullptr;
+    float* past = row + hidden;
+    // the earlier inputs come in beside the row: loads that wait for nothing, none of them behind a store to the state
+    for (int j = 0; j < kept; ++j) {
+        const bool before_start = pos - (kept - j) < 0;
+        for (int c = threadIdx.x; c < hidden; c += LNC_THREADS) past[(size_t)j * hidden + c] = before_start ? 0.f : mine[(size_t)j * hidden + c];
+    }
+    const bool sums = threadIdx.x < LN_THREADS;
+    float sum = 0.f;
+    if (sums)
+        for (int i = threadIdx.x; i < hidden; i += LN_THREADS) {
+            float v = hrow[i];
+            if (has_delta) {
+                v = fmaf(delta_scale, to_float(drow[i]), v);
+                hrow[i] = v;
+            }
+            row[i] = v;
+            sum += v;
+        }
+    const float mean = block_sum(sum, scratch) / (float)hidden;
+    float ss = 0.f;
+    if (sums)
+        for (int i = threadIdx.x; i < hidden; i += LN_THREADS) {
+            const float dev = row[i] - mean;
+            ss = fmaf(dev, dev, ss);
+        }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    TO* orow = out + (size_t)t * hidden;
+    // (the block-wide sums above are the barrier between the writes of `row` and `past` and these reads)
+    for (int c = threadIdx.x; c < hidden; c += LNC_THREADS) {
+        const float own = (row[c] - mean) * inv * w[c];
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) acc = fmaf(cw[(size_t)j * hidden + c], j == kept ? own : past[(size_t)j * hidden + c], acc);
+        orow[c] = from_float<TO>(own + acc);
+        if (update && kept > 0) {
+            // positions before the sequence's start stay zeros in the state, as they are where nothing was written yet
+            for (int k = 0; k + 1 < kept; ++k) mine[(size_t)k * hidden + c] = past[(size_t)(k + 1) * hidden + c];
+            mine[(size_t)(kept - 1) * hidden + c] = own;
+        }
+    }
+}
+
 // out = sa * a + sb * b, element by element, in 32-bit
 template <typename T>
 __global__ void scaled_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b, float sb, float* __restrict__ out,
@@ -117,6 +183,32 @@ GK_EXPORT int gk_add_layernorm(float* h, const void* delta, int delta_dtype, flo
         })
     })
     GK_CHECK_LAUNCH("add_layernorm");
+    return GK_OK;
+}
+
+// weight [hidden] and conv_w [taps, hidden] 32-bit; state [n_slots, taps - 1, hidden] (may be null for one tap); one row a
+// sequence.
+GK_EXPORT int gk_add_layernorm_conv_single(float* h, const void* delta, int delta_dtype, float delta_scale, const float* weight,
+                                           const float* conv_w, float* state, const int* tok_pos, const int* tok_seq, const int* slots,
+                                           void* out, int out_dtype, int n_rows, int hidden, int taps, float eps, int update,
+                                           void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(delta_dtype) && GK_VALID_DTYPE(out_dtype), "add_layernorm_conv_single: bad dtype code");
+    GK_REQUIRE(n_rows >= 0 && hidden > 0 && taps >= 1, "add_layernorm_conv_single: bad sizes");
+    GK_REQUIRE(taps == 1 || state != nullptr, "add_layernorm_conv_single: %d taps need the sequences' states", taps);
+    GK_REQUIRE(eps > 0.f, "add_layernorm_conv_single: eps must be positive");
+    const size_t smem = (size_t)hidden * taps * sizeof(float);
+    GK_REQUIRE(smem <= 200 * 1024, "add_layernorm_conv_single: rows of %d with %d taps do not fit in shared memory", hidden, taps);
+    if (n_rows == 0) return GK_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    GK_DISPATCH_DTYPE(delta_dtype, TD, {
+        GK_DISPATCH_DTYPE(out_dtype, TO, {
+            if (smem > 48 * 1024)
+                cudaFuncSetAttribute(add_layernorm_conv_single_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            gk_launch(add_layernorm_conv_single_kernel<TD, TO>, dim3(n_rows), dim3(LNC_THREADS), smem, s, h, (const TD*)delta, delta_scale,
+                      weight, conv_w, state, tok_pos, tok_seq, slots, (TO*)out, hidden, taps, eps, update);
+        })
+    })
+    GK_CHECK_LAUNCH("add_layernorm_conv_single");
     return GK_OK;
 }
 

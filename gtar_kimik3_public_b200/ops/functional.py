@@ -1503,6 +1503,42 @@ def add_layernorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Ten
     return out
 
 
+def add_layernorm_conv_single(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, conv_weight: torch.Tensor,
+                              state: torch.Tensor | None, tok_pos: torch.Tensor, tok_seq: torch.Tensor, slots: torch.Tensor,
+                              out_dtype: torch.dtype, delta_scale: float = 1.0, update_state: bool = True) -> torch.Tensor:
+    """:func:`add_layernorm` and :func:`causal_conv` behind it in one kernel, for steps in which every sequence brings one
+    token (row ``t`` belongs to sequence ``tok_seq[t]``): ``h += delta_scale * delta``, ``y = layernorm(h)``, returns
+    ``y + conv(y)`` with the earlier inputs from ``state [n_slots, taps - 1, width]``, which is moved on by ``y`` when
+    ``update_state``.  The same numbers as the two kernels one after the other."""
+    require_device(h.device)
+    _check(h, "h", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    _check(conv_weight, "conv_weight", torch.float32, 2)
+    n, hidden = h.shape
+    taps = conv_weight.shape[0]
+    if weight.shape[0] != hidden or conv_weight.shape[1] != hidden:
+        raise KernelError(f"norm weight of {weight.shape[0]} and convolution weights {tuple(conv_weight.shape)} for rows of {hidden}")
+    delta_code = 0
+    if delta is not None:
+        _check(delta, "delta", dims=2)
+        if delta.shape != h.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+        delta_code = dtype_code(delta.dtype)
+    if taps > 1:
+        _check(state, "state", torch.float32, 3)
+        if tuple(state.shape[1:]) != (taps - 1, hidden):
+            raise KernelError(f"state {tuple(state.shape)} does not hold {taps - 1} inputs of width {hidden}")
+    for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    if tok_pos.shape[0] < n or tok_seq.shape[0] < n:
+        raise KernelError("add_layernorm_conv_single: fewer positions than rows")
+    out = torch.empty((n, hidden), dtype=out_dtype, device=h.device)
+    call("gk_add_layernorm_conv_single", ptr(h), ptr(delta), delta_code, float(delta_scale), ptr(weight), ptr(conv_weight),
+         ptr(state) if taps > 1 else None, ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(out), dtype_code(out_dtype), n, hidden, taps,
+         float(eps), int(bool(update_state)), stream_ptr())
+    return out
+
+
 def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float) -> torch.Tensor:
     """``scale_a * a + scale_b * b`` in 32-bit, element by element."""
     require_device(a.device)

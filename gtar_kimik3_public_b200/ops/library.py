@@ -80,6 +80,7 @@ _SIGNATURES: dict[str, list] = {
     "gk_sigmoid_gate": [P, P, L, P, I, L, I, P],
     "gk_softcap": [P, L, F, P],
     "gk_add_layernorm": [P, P, I, F, P, I, P, I, P, I, I, F, P],
+    "gk_add_layernorm_conv_single": [P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, F, I, P],
     "gk_scaled_sum": [P, F, P, F, I, P, L, P],
     "gk_relu_squared": [P, P, I, L, P],
     "gk_scale": [P, L, F, P],

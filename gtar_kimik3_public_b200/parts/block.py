@@ -161,6 +161,14 @@ class ConvPreNormBlock(Block):
             return own
         return [*request, *own] if isinstance(request, (list, tuple)) else [request, *own]
 
+    def _normed_through_conv(self, norm, h, pending, weight, state, ctx: StepContext):
+        """``norm(h + pending)`` through the convolution; one kernel where every sequence brings one token and the norm has
+        that form, else the norm's kernel and the convolution's."""
+        if ctx.all_single and hasattr(norm, "forward_conv_single"):
+            keep = state is not None and not ctx.extras.get("cache_read_only", False)
+            return norm.forward_conv_single(h, pending, weight, state, ctx, keep)
+        return self._through_conv(norm.forward(h, pending, torch.float32), weight, state, ctx)
+
     def _through_conv(self, a, weight, state, ctx: StepContext):
         keep = state is not None and not ctx.extras.get("cache_read_only", False)
         # one token a sequence: the convolution's kernel moves the states on itself
@@ -180,14 +188,14 @@ class ConvPreNormBlock(Block):
             views = views[:len(views) - n_own]
             cache = tuple(views) if isinstance(mixer_request, (list, tuple)) else (views[0] if views else None)
         if self.conv_taps:
-            a = self._through_conv(self.norm_1.forward(h, pending, torch.float32), self.conv_1, states[0], ctx)
+            a = self._normed_through_conv(self.norm_1, h, pending, self.conv_1, states[0], ctx)
         else:
             a = self.norm_1.forward(h, pending, ctx.dtype)
         branch = self.mixer.forward(a, ctx, cache)
         if self.feed_forward is None:
             return h, branch
         if self.conv_taps:
-            b = self._through_conv(self.norm_2.forward(h, branch, torch.float32), self.conv_2, states[1], ctx)
+            b = self._normed_through_conv(self.norm_2, h, branch, self.conv_2, states[1], ctx)
         else:
             b = self.norm_2.forward(h, branch, ctx.dtype)
         return h, self.feed_forward.forward(b, ctx)

@@ -69,5 +69,10 @@ class LayerNorm(Norm):
     def forward(self, h, delta, out_dtype, rows=None):
         return F.add_layernorm(h, delta, self.weight, self.eps, out_dtype, rows, self.delta_scale)
 
+    def forward_conv_single(self, h, delta, conv_weight, state, ctx, update_state: bool):
+        """The norm and the short convolution over time behind it as one kernel, in steps of one token a sequence."""
+        return F.add_layernorm_conv_single(h, delta, self.weight, self.eps, conv_weight, state, ctx.tok_pos, ctx.tok_seq, ctx.slots,
+                                           ctx.dtype, self.delta_scale, update_state)
+
 
 register_part("norm", "layernorm", LayerNorm)

@@ -96,6 +96,53 @@ def test_time_convolution_in_portions(taps, cuts):
     assert (torch.cat(got).double().cpu() - want).abs().max().item() < 1e-5
 
 
+@pytest.mark.parametrize("taps,width,out_dtype", [(4, 40, torch.float32), (2, 72, torch.bfloat16), (1, 24, torch.float32),
+                                                  (5, 2056, torch.float32)])
+def test_norm_and_time_convolution_in_one_kernel_token_by_token(taps, width, out_dtype):
+    """Three sequences of unequal age, one token each a step, in slots that are not in order: the stream gets the scaled
+    branch, and what comes out is the plain norm through the plain convolution over each sequence's whole past."""
+    steps, starts, slots = 9, [0, 2, 5], [3, 0, 2]
+    gen = torch.Generator(device=DEV).manual_seed(taps * 100 + width)
+    norm_w = 1.0 + 0.2 * torch.randn(width, generator=gen, device=DEV)
+    w = torch.randn(width, taps, generator=gen, device=DEV) * 0.5
+    weight = w.t().contiguous()
+    state = torch.full((4, taps - 1, width), float("nan"), device=DEV) if taps > 1 else None
+    # the rows every sequence has seen before its first step here, through the unfused kernels
+    past = [torch.randn(n, width, generator=gen, device=DEV) * 2.0 + 0.5 for n in starts]
+    normed = [[] for _ in starts]
+    for s, rows in enumerate(past):
+        if state is not None:
+            state[slots[s]] = 0.0
+        if rows.shape[0]:
+            y = F().add_layernorm(rows.clone(), None, norm_w, 1e-5, torch.float32)
+            normed[s].append(y)
+            if state is not None:
+                F().conv_state(y, state, _i32([0, rows.shape[0]]), _i32([slots[s]]), 1)
+    outs = [[] for _ in starts]
+    for step in range(steps):
+        h = torch.randn(len(starts), width, generator=gen, device=DEV) * 2.0 + 0.5
+        delta = torch.randn(len(starts), width, generator=gen, device=DEV).to(out_dtype)
+        summed = h.double() + 0.4 * delta.double()
+        pos, seq, _ = _layout([1] * len(starts), [at + step for at in starts])
+        frozen = state.clone() if state is not None else None
+        peek = F().add_layernorm_conv_single(h.clone(), delta, norm_w, 1e-5, weight, state, pos, seq, _i32(slots), out_dtype,
+                                             delta_scale=0.4, update_state=False)
+        if state is not None:
+            assert torch.equal(state[slots], frozen[slots]), "a read-only step moved the states"
+        stream = h.clone()
+        got = F().add_layernorm_conv_single(stream, delta, norm_w, 1e-5, weight, state, pos, seq, _i32(slots), out_dtype,
+                                            delta_scale=0.4)
+        assert torch.equal(got, peek)
+        assert torch.allclose(stream.double(), summed, atol=1e-6), "the stream does not hold the sum"
+        for s in range(len(starts)):
+            normed[s].append(plain.layer_norm(summed[s:s + 1].cpu(), norm_w.double().cpu(), 1e-5).to(DEV))
+            outs[s].append(got[s])
+    tol = 3e-5 if out_dtype == torch.float32 else 4e-2
+    for s in range(len(starts)):
+        want = plain.with_time_conv(torch.cat(normed[s]).double().cpu(), w.double().cpu())[starts[s]:]
+        assert (torch.stack(outs[s]).double().cpu() - want).abs().max().item() < tol, f"sequence {s}"
+
+
 # ------------------------------------------------------------------ between the projection and the core
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("n_q,n_k,d,dv,rot,divisor,silu,unit,k_scale", [
