@@ -57,28 +57,40 @@ __global__ void __launch_bounds__(LN_THREADS) add_layernorm_kernel(float* __rest
 // of the earlier inputs and for the convolution, a channel or two a thread, and its first LN_THREADS threads alone sum
 // the row, as the norm's own kernel does (the others add zeros, which a sum over the warps does not see).
 constexpr int LNC_THREADS = 1024;
+__device__ __forceinline__ void lnc_copy4(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(LNC_THREADS) add_layernorm_conv_single_kernel(
     float* __restrict__ h, const TD* __restrict__ delta, float delta_scale, const float* __restrict__ w, const float* __restrict__ cw,
     float* __restrict__ state, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
     TO* __restrict__ out, int hidden, int taps, float eps, int update) {
-    extern __shared__ float row[];  // hidden floats, then the sequence's taps - 1 earlier inputs [taps - 1, hidden]
+    extern __shared__ float row[];  // hidden floats; the sequence's taps - 1 earlier inputs; the taps' weights; the norm's
     __shared__ float scratch[33];
     pdl_launch_dependents();
-    pdl_wait();
     const int t = blockIdx.x;
+    const int kept = taps - 1;
+    float* past = row + hidden;                   // [kept, hidden]
+    float* cws = past + (size_t)kept * hidden;    // [taps, hidden]
+    float* ws = cws + (size_t)taps * hidden;      // [hidden]
+    // Everything but the row itself comes in by asynchronous copies that no instruction waits for before the last loop:
+    // the weights first (they wait for no earlier kernel), then the earlier inputs, whose place hangs on two index loads.
+    for (int i = threadIdx.x; i < taps * hidden; i += LNC_THREADS) lnc_copy4(cws + i, cw + i);
+    for (int i = threadIdx.x; i < hidden; i += LNC_THREADS) lnc_copy4(ws + i, w + i);
+    pdl_wait();
     float* hrow = h + (size_t)t * hidden;
     const bool has_delta = delta != nullptr;
     const TD* drow = delta + (size_t)t * hidden;
     const int pos = tok_pos[t];
-    const int kept = taps - 1;
     float* mine = kept > 0 ? state + (size_t)slots[tok_seq[t]] * kept * hidden : nullptr;
-    float* past = row + hidden;
-    // the earlier inputs come in beside the row: loads that wait for nothing, none of them behind a store to the state
     for (int j = 0; j < kept; ++j) {
-        const bool before_start = pos - (kept - j) < 0;
-        for (int c = threadIdx.x; c < hidden; c += LNC_THREADS) past[(size_t)j * hidden + c] = before_start ? 0.f : mine[(size_t)j * hidden + c];
+        if (pos - (kept - j) < 0) {  // before the sequence's start
+            for (int c = threadIdx.x; c < hidden; c += LNC_THREADS) past[(size_t)j * hidden + c] = 0.f;
+        } else {
+            for (int c = threadIdx.x; c < hidden; c += LNC_THREADS) lnc_copy4(past + (size_t)j * hidden + c, mine + (size_t)j * hidden + c);
+        }
     }
+    asm volatile("cp.async.commit_group;\n" ::);
     const bool sums = threadIdx.x < LN_THREADS;
     float sum = 0.f;
     if (sums)
@@ -100,11 +112,12 @@ __global__ void __launch_bounds__(LNC_THREADS) add_layernorm_conv_single_kernel(
         }
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
     TO* orow = out + (size_t)t * hidden;
-    // (the block-wide sums above are the barrier between the writes of `row` and `past` and these reads)
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
     for (int c = threadIdx.x; c < hidden; c += LNC_THREADS) {
-        const float own = (row[c] - mean) * inv * w[c];
+        const float own = (row[c] - mean) * inv * ws[c];
         float acc = 0.f;
-        for (int j = 0; j < taps; ++j) acc = fmaf(cw[(size_t)j * hidden + c], j == kept ? own : past[(size_t)j * hidden + c], acc);
+        for (int j = 0; j < taps; ++j) acc = fmaf(cws[(size_t)j * hidden + c], j == kept ? own : past[(size_t)j * hidden + c], acc);
         orow[c] = from_float<TO>(own + acc);
         if (update && kept > 0) {
             // positions before the sequence's start stay zeros in the state, as they are where nothing was written yet
@@ -186,6 +199,9 @@ GK_EXPORT int gk_add_layernorm(float* h, const void* delta, int delta_dtype, flo
     return GK_OK;
 }
 
+// The row, its earlier inputs and the weights stay in shared memory: 2 taps + 1 rows of 32-bit numbers within this.
+constexpr int GK_ADD_LAYERNORM_CONV_SINGLE_SMEM = 200 * 1024;
+
 // weight [hidden] and conv_w [taps, hidden] 32-bit; state [n_slots, taps - 1, hidden] (may be null for one tap); one row a
 // sequence.
 GK_EXPORT int gk_add_layernorm_conv_single(float* h, const void* delta, int delta_dtype, float delta_scale, const float* weight,
@@ -196,8 +212,8 @@ GK_EXPORT int gk_add_layernorm_conv_single(float* h, const void* delta, int delt
     GK_REQUIRE(n_rows >= 0 && hidden > 0 && taps >= 1, "add_layernorm_conv_single: bad sizes");
     GK_REQUIRE(taps == 1 || state != nullptr, "add_layernorm_conv_single: %d taps need the sequences' states", taps);
     GK_REQUIRE(eps > 0.f, "add_layernorm_conv_single: eps must be positive");
-    const size_t smem = (size_t)hidden * taps * sizeof(float);
-    GK_REQUIRE(smem <= 200 * 1024, "add_layernorm_conv_single: rows of %d with %d taps do not fit in shared memory", hidden, taps);
+    const size_t smem = (size_t)hidden * (2 * taps + 1) * sizeof(float);
+    GK_REQUIRE(smem <= (size_t)GK_ADD_LAYERNORM_CONV_SINGLE_SMEM, "add_layernorm_conv_single: rows of %d with %d taps do not fit in shared memory", hidden, taps);
     if (n_rows == 0) return GK_OK;
     cudaStream_t s = (cudaStream_t)stream;
     GK_DISPATCH_DTYPE(delta_dtype, TD, {

@@ -1503,6 +1503,12 @@ def add_layernorm(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Ten
     return out
 
 
+def add_layernorm_conv_single_fits(hidden: int, taps: int) -> bool:
+    """Whether :func:`add_layernorm_conv_single` takes rows of this width: the row, its ``taps - 1`` earlier inputs and the
+    weights of the norm and of the taps within 200 KB of shared memory (the kernel's own rule)."""
+    return hidden > 0 and taps >= 1 and hidden * (2 * taps + 1) * 4 <= 200 * 1024
+
+
 def add_layernorm_conv_single(h: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, conv_weight: torch.Tensor,
                               state: torch.Tensor | None, tok_pos: torch.Tensor, tok_seq: torch.Tensor, slots: torch.Tensor,
                               out_dtype: torch.dtype, delta_scale: float = 1.0, update_state: bool = True) -> torch.Tensor:

@@ -164,7 +164,7 @@ class ConvPreNormBlock(Block):
     def _normed_through_conv(self, norm, h, pending, weight, state, ctx: StepContext):
         """``norm(h + pending)`` through the convolution; one kernel where every sequence brings one token and the norm has
         that form, else the norm's kernel and the convolution's."""
-        if ctx.all_single and hasattr(norm, "forward_conv_single"):
+        if ctx.all_single and hasattr(norm, "forward_conv_single") and F.add_layernorm_conv_single_fits(h.shape[1], weight.shape[0]):
             keep = state is not None and not ctx.extras.get("cache_read_only", False)
             return norm.forward_conv_single(h, pending, weight, state, ctx, keep)
         return self._through_conv(norm.forward(h, pending, torch.float32), weight, state, ctx)
