@@ -1111,6 +1111,11 @@ def _rezulorn_kernel_table(d: dict, t: dict, peak: dict) -> dict:
         ms = _event_ms(lambda: F.causal_conv(normed, conv_w, conv_state, tok_pos, tok_seq, cu_q, slots, bf, update_single_token_state=n_seqs > 1),
                        flush=flush, inner=inner)
         record(f"rezulorn convolution over time, {label}", ms, tokens * w * (4 + 2) + (n_seqs * 3 * w * 8 if n_seqs > 1 else 0))
+        if n_seqs > 1:  # what single-token steps run instead of the two above
+            ms = _event_ms(lambda: F.add_layernorm_conv_single(hs, branch, wn, 1e-5, conv_w, conv_state, tok_pos, tok_seq, slots, bf,
+                                                               delta_scale=0.5), flush=flush, inner=inner)
+            record(f"rezulorn residual add, layer norm and convolution in one kernel, {label}", ms,
+                   tokens * w * (4 + 2 + 4 + 2) + n_seqs * 3 * w * 8)
         ms = _event_ms(lambda: F.scaled_sum(branch, 0.6, branch, 0.9), flush=flush, inner=inner)
         record(f"rezulorn sum of a pair's branches, {label}", ms, tokens * w * (2 + 2 + 4))
         # ---- the recurrence with a fixed decay, beside the delta rule at the same heads

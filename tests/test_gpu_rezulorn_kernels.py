@@ -629,3 +629,4 @@ def test_scored_attention_parts_rule():
     assert parts(8, 16, 4, 1, 33, 148) > 1                # single tokens do not
     assert parts(8, 16, 4, 1, 1, 148) == 1                # never more parts than pages
     assert parts(1, 2, 1, 1, 1000, 148) <= 32
+    assert 8 * 4 * parts(8, 16, 4, 1, 33, 148) <= 2 * 148  # the blocks stay within two a multiprocessor
