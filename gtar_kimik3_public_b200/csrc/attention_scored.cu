@@ -7,6 +7,13 @@
 //   weights = softmax over the visible keys:   o = sum_j softmax(s)_j v_j
 //   weights = sigmoid:                         o = sum_j sigmoid(s_j + bias_h) v_j      (no sum over keys divides)
 // A key that the window has left and the first tokens keep stays at its true position.
+// Further rules, each present only where its argument is given:
+//   chunk > 0:   a key is visible only from its own chunk, floor(i / chunk) = floor(j / chunk), chunks counted from
+//                the sequence's first position
+//   temp:        a number per query head on the product:  (q . k_j) * scale * temp_h
+//   dist_bias:   a table [n_dist, n_q] of terms ADDED to the score, read at row min(i - j, n_dist - 1)
+//   sink:        a number per query head whose exponential joins the softmax's denominator (and nothing else):
+//                weights_j = exp(s_j) / (exp(sink_h) + sum_visible exp(s))
 //
 // One warp per (token, query head).  Keys are taken in blocks of 32 from key 0 upward, one key per lane; blocks
 // that hold no visible key are passed over.  All sums are 32-bit, and the sequence of operations for a (token,
@@ -66,7 +73,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_scored_kernel(
     const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
     const int* __restrict__ block_table, int n_tokens, int n_q, int n_kv, int d, int dv, int max_pages, int page_size,
     float scale, int window, int keep_first, const float* __restrict__ r1, const float* __restrict__ r2,
-    const float* __restrict__ head_bias) {
+    const float* __restrict__ head_bias, int chunk, const float* __restrict__ temp, const float* __restrict__ dist_bias,
+    int n_dist, const float* __restrict__ sink) {
     extern __shared__ float q_smem[];  // WARPS * d
     pdl_launch_dependents();
     pdl_wait();
@@ -86,8 +94,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_scored_kernel(
     const float b1 = biased ? r1[hq] : 0.f, b2 = biased ? r2[hq] : 0.f;
     const float add = head_bias != nullptr ? head_bias[hq] : 0.f;
 
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;  // first key of the window
-    float m = -INFINITY, l = 0.f;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;  // first key of the window
+    if (chunk > 0) {
+        const int first = (pos / chunk) * chunk;  // first key of the token's chunk
+        if (first > 0) keep_first = 0;            // the kept first keys lie in an earlier chunk
+        lo = max(lo, first);
+    }
+    if (temp != nullptr) scale *= temp[hq];
+    // the sink opens the running softmax: a term exp(sink) in the denominator that carries no value
+    float m = (!SIGMOID && sink != nullptr) ? sink[hq] : -INFINITY, l = (!SIGMOID && sink != nullptr) ? 1.f : 0.f;
     float acc[MAX_ACC];
 #pragma unroll
     for (int c = 0; c < MAX_ACC; ++c) acc[c] = 0.f;
@@ -107,6 +122,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_scored_kernel(
         if (valid) {
             s = dot_row<T>(qs, k_pages + (row0 + lane) * d, d) * scale;
             if (biased) s -= b1 * log1pf(b2 * (float)(pos - j));
+            if (dist_bias != nullptr) s += dist_bias[(size_t)min(pos - j, n_dist - 1) * n_q + hq];
         }
         float p;
         if (SIGMOID) {
@@ -148,7 +164,8 @@ GK_EXPORT int gk_attention_scored_exact(const void* q, const void* k_pages, cons
                                         const int* tok_pos, const int* tok_seq, const int* slots, const int* block_table,
                                         int n_tokens, int n_q, int n_kv, int d, int dv, int max_pages, int page_size, float scale,
                                         int window, int keep_first, const float* r1, const float* r2, const float* head_bias,
-                                        int weights, void* stream) {
+                                        int weights, int chunk, const float* temp, const float* dist_bias, int n_dist,
+                                        const float* sink, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype), "attention_scored: bad dtype %d", dtype);
     GK_REQUIRE(n_tokens >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_scored: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(d > 0 && dv > 0 && dv <= 32 * MAX_ACC, "attention_scored: keys of %d must be positive, values of %d at most %d", d, dv,
@@ -157,6 +174,8 @@ GK_EXPORT int gk_attention_scored_exact(const void* q, const void* k_pages, cons
     GK_REQUIRE(window >= 0 && keep_first >= 0, "attention_scored: window and kept first keys must be >= 0 (0 = none)");
     GK_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_scored: the distance term needs both of its numbers");
     GK_REQUIRE(weights == 0 || weights == 1, "attention_scored: weights are softmax (0) or sigmoid (1)");
+    GK_REQUIRE(chunk >= 0 && (dist_bias == nullptr || n_dist > 0), "attention_scored: bad chunk or distance table");
+    GK_REQUIRE(sink == nullptr || weights == 0, "attention_scored: a sink belongs to the softmax");
     if (n_tokens == 0) return GK_OK;
     const long long warps = (long long)n_tokens * n_q;
     const long long blocks = (warps + WARPS - 1) / WARPS;
@@ -167,11 +186,11 @@ GK_EXPORT int gk_attention_scored_exact(const void* q, const void* k_pages, cons
         if (weights == 1)
             gk_launch(attention_scored_kernel<T, true>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, s, (const T*)q, (const T*)k_pages,
                       (const T*)v_pages, (T*)out, tok_pos, tok_seq, slots, block_table, n_tokens, n_q, n_kv, d, dv, max_pages, page_size,
-                      scale, window, keep_first, r1, r2, head_bias);
+                      scale, window, keep_first, r1, r2, head_bias, chunk, temp, dist_bias, n_dist, sink);
         else
             gk_launch(attention_scored_kernel<T, false>, dim3((unsigned)blocks), dim3(WARPS * 32), smem, s, (const T*)q, (const T*)k_pages,
                       (const T*)v_pages, (T*)out, tok_pos, tok_seq, slots, block_table, n_tokens, n_q, n_kv, d, dv, max_pages, page_size,
-                      scale, window, keep_first, r1, r2, head_bias);
+                      scale, window, keep_first, r1, r2, head_bias, chunk, temp, dist_bias, n_dist, sink);
     })
     GK_CHECK_LAUNCH("attention_scored");
     return GK_OK;

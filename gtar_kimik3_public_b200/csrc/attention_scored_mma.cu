@@ -4,6 +4,10 @@
 //   visible:  j <= i  and  (window = 0  or  i - j < window  or  j < keep_first)
 //   s_j = (q . k_j) * scale - r1_h * ln(1 + r2_h * (i - j))          (the second term only where r1, r2 are given)
 //   softmax: o = sum_j softmax(s)_j v_j          sigmoid: o = sum_j sigmoid(s_j + bias_h) v_j
+// and, each only where its argument is given: keys of the token's own chunk only (chunks of `chunk` positions counted
+// from the sequence's start), a number per query head on the product (temp), a table [n_dist, n_q] of terms added to
+// the score by distance (row min(i - j, n_dist - 1)), a number per query head whose exponential joins the softmax's
+// denominator and carries no value (sink).
 //
 // The rows of a block's tile are (token, query head of one kv group) pairs, token-major, so the query heads that
 // share a kv head share every loaded page; a warp owns 16 rows and K and V pages stream through a three-stage
@@ -46,7 +50,8 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ cu_q,
     const int* __restrict__ kv_len, const int* __restrict__ slots, const int* __restrict__ block_table, int n_tokens, int n_q,
     int n_kv, int max_pages, float sl2, int window, int keep_first, const float* __restrict__ r1, const float* __restrict__ r2,
-    const float* __restrict__ head_bias, int n_split) {
+    const float* __restrict__ head_bias, int n_split, int chunk, const float* __restrict__ temp,
+    const float* __restrict__ dist_bias, int n_dist, const float* __restrict__ sink) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     ScoredSmem<D>& sm = *reinterpret_cast<ScoredSmem<D>*>(smem_raw);
     pdl_launch_dependents();
@@ -66,7 +71,8 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     const int wrow0 = row0 + warp * 16;
     int tok[2], pos[2], head[2];
     bool row_ok[2];
-    float b1[2], b2[2], add[2];
+    float b1[2], b2[2], add[2], sl2h[2];
+    int first[2];  // first key of the row's chunk
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = wrow0 + (lane >> 2) + 8 * h;
@@ -74,6 +80,8 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
         tok[h] = row_ok[h] ? r / group : 0;
         pos[h] = past + tok[h];
         head[h] = hk * group + (row_ok[h] ? r % group : 0);
+        first[h] = chunk > 0 ? (pos[h] / chunk) * chunk : 0;
+        sl2h[h] = temp != nullptr ? sl2 * temp[head[h]] : sl2;
         b1[h] = r1 != nullptr ? r1[head[h]] : 0.f;  // the distance term in the base-2 domain: r1 log2(1 + r2 gap)
         b2[h] = r1 != nullptr ? r2[head[h]] : 0.f;
         add[h] = head_bias != nullptr ? head_bias[head[h]] * LOG2E : 0.f;
@@ -97,7 +105,12 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     const int last_row = min(row0 + SC_ROWS, n_rows) - 1;
     const int max_pos = past + last_row / group;
     const int min_pos = past + row0 / group;
-    const int lo_block = (window > 0 && min_pos - window + 1 > 0) ? min_pos - window + 1 : 0;
+    int lo_block = (window > 0 && min_pos - window + 1 > 0) ? min_pos - window + 1 : 0;
+    if (chunk > 0) {
+        const int chunk_first = (min_pos / chunk) * chunk;  // no row of the block sees a key before its first row's chunk
+        if (chunk_first > 0) keep_first = 0;                // the kept first keys lie in an earlier chunk
+        lo_block = max(lo_block, chunk_first);
+    }
     const int p_begin = lo_block / PAGE, p_end = max_pos / PAGE + 1;
     const int kept_pages = window > 0 ? min((keep_first + PAGE - 1) / PAGE, p_begin) : 0;
     const int n_iter = kept_pages + p_end - p_begin;
@@ -106,7 +119,8 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     const int w_last_row = min(wrow0 + 16, n_rows) - 1;
     const int w_max_pos = w_last_row >= wrow0 ? past + w_last_row / group : -1;
     const int w_min_pos = past + wrow0 / group;
-    const int w_lo = (window > 0 && w_min_pos - window + 1 > 0) ? w_min_pos - window + 1 : 0;
+    int w_lo = (window > 0 && w_min_pos - window + 1 > 0) ? w_min_pos - window + 1 : 0;
+    if (chunk > 0) w_lo = max(w_lo, (w_min_pos / chunk) * chunk);
 
     auto page_index = [&](int it) { return it < kept_pages ? it : p_begin + it - kept_pages; };
     auto issue = [&](int it) {
@@ -123,6 +137,14 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     };
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (!SIGMOID && sink != nullptr && split == 0) {
+        // the sink opens the running softmax of the first part: a term exp(sink) in the denominator that carries no value
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m[h] = sink[head[h]] * LOG2E;
+            l[h] = 1.f;
+        }
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j)
@@ -151,9 +173,11 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int gap = pos[h] - key;
-                        const bool hidden = gap < 0 || (window > 0 && gap >= window && key >= keep_first);
-                        float t = s[n][2 * h + c] * sl2;
+                        const bool hidden = gap < 0 || (window > 0 && gap >= window && key >= keep_first) || key < first[h];
+                        float t = s[n][2 * h + c] * sl2h[h];
                         if (biased) t -= b1[h] * lg2_fast(fmaf(b2[h], (float)max(gap, 0), 1.f));
+                        if (dist_bias != nullptr)
+                            t = fmaf(__ldg(dist_bias + (size_t)min(max(gap, 0), n_dist - 1) * n_q + head[h]), LOG2E, t);
                         if (SIGMOID)
                             s[n][2 * h + c] = hidden ? 0.f : __fdividef(1.f, 1.f + exp2_fast(-(t + add[h])));
                         else
@@ -235,7 +259,8 @@ template <int D, bool SIGMOID>
 int launch_scored(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml, const int* cu_q,
                   const int* kv_len, const int* slots, const int* block_table, int n_seqs, int max_q_len, int n_tokens, int n_q,
                   int n_kv, int max_pages, float scale, int window, int keep_first, const float* r1, const float* r2,
-                  const float* head_bias, int n_split, cudaStream_t stream) {
+                  const float* head_bias, int n_split, int chunk, const float* temp, const float* dist_bias, int n_dist,
+                  const float* sink, cudaStream_t stream) {
     const size_t smem = sizeof(ScoredSmem<D>);
     static bool configured = false;
     if (!configured) {
@@ -249,7 +274,7 @@ int launch_scored(const void* q, const void* k_pages, const void* v_pages, void*
     gk_launch(attention_scored_mma_kernel<D, SIGMOID>, dim3((unsigned)blocks, n_kv, n_seqs), dim3(SC_WARPS * 32), smem, stream,
               (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, part_o, part_ml,
               cu_q, kv_len, slots, block_table, n_tokens, n_q, n_kv, max_pages, scale * LOG2E, window, keep_first, r1, r2, head_bias,
-              n_split);
+              n_split, chunk, temp, dist_bias, n_dist, sink);
     GK_CHECK_LAUNCH("attention_scored_mma");
     if (n_split > 1) {
         const long long items = (long long)n_tokens * n_q;
@@ -270,7 +295,8 @@ GK_EXPORT int gk_attention_scored_bf16(const void* q, const void* k_pages, const
                                        float* part_ml, const int* cu_q, const int* kv_len, const int* slots, const int* block_table,
                                        int n_seqs, int max_q_len, int n_tokens, int n_q, int n_kv, int head_dim, int max_pages,
                                        int page_size, float scale, int window, int keep_first, const float* r1, const float* r2,
-                                       const float* head_bias, int weights, int n_split, void* stream) {
+                                       const float* head_bias, int weights, int n_split, int chunk, const float* temp,
+                                       const float* dist_bias, int n_dist, const float* sink, void* stream) {
     GK_REQUIRE(n_seqs >= 0 && n_q > 0 && n_kv > 0 && n_q % n_kv == 0, "attention_scored_mma: bad head counts %d/%d", n_q, n_kv);
     GK_REQUIRE(page_size == attn::PAGE, "attention_scored_mma: page_size must be %d, got %d", attn::PAGE, page_size);
     GK_REQUIRE(head_dim == 64 || head_dim == 128, "attention_scored_mma: head size %d is not 64 or 128 (use the exact kernel)", head_dim);
@@ -280,11 +306,14 @@ GK_EXPORT int gk_attention_scored_bf16(const void* q, const void* k_pages, const
     GK_REQUIRE(weights == 0 || weights == 1, "attention_scored_mma: weights are softmax (0) or sigmoid (1)");
     GK_REQUIRE(n_split >= 1 && (n_split == 1 || (part_o != nullptr && (weights == 1 || part_ml != nullptr))),
                "attention_scored_mma: %d parts need their workspaces", n_split);
+    GK_REQUIRE(chunk >= 0 && (dist_bias == nullptr || n_dist > 0), "attention_scored_mma: bad chunk or distance table");
+    GK_REQUIRE(sink == nullptr || weights == 0, "attention_scored_mma: a sink belongs to the softmax");
     if (n_seqs == 0 || max_q_len == 0 || n_tokens == 0) return GK_OK;
     cudaStream_t s = (cudaStream_t)stream;
 #define GK_SCORED(D, SIG)                                                                                                             \
     return launch_scored<D, SIG>(q, k_pages, v_pages, out, part_o, part_ml, cu_q, kv_len, slots, block_table, n_seqs, max_q_len,      \
-                                 n_tokens, n_q, n_kv, max_pages, scale, window, keep_first, r1, r2, head_bias, n_split, s)
+                                 n_tokens, n_q, n_kv, max_pages, scale, window, keep_first, r1, r2, head_bias, n_split, chunk, temp,  \
+                                 dist_bias, n_dist, sink, s)
     if (head_dim == 64) {
         if (weights == 1) GK_SCORED(64, true);
         GK_SCORED(64, false);

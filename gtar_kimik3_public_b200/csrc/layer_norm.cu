@@ -173,6 +173,37 @@ __global__ void relu_squared_bf16x8_kernel(const uint4* __restrict__ in, uint4* 
     out[idx] = raw;
 }
 
+// A quadratic above zero and an exponential below, joined smoothly at zero:
+//   z > 0:  up * z^2 + z / 2          z <= 0:  down * (exp(z) - 1 - z) + z / 2
+// `up` and `down` are the two finished constants (the caller forms them from the stored numbers once, at load).
+__device__ __forceinline__ float xielu_f(float z, float up, float down) {
+    return z > 0.f ? fmaf(up * z, z, 0.5f * z) : fmaf(down, expm1f(z) - z, 0.5f * z);
+}
+
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ in, T* __restrict__ out, long long total, float up, float down) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    out[idx] = from_float<T>(xielu_f(to_float(in[idx]), up, down));
+}
+
+__global__ void xielu_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, long long pieces, float up, float down) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= pieces) return;
+    uint4 raw = in[idx];
+    __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 v = __bfloat1622float2(pair[i]);
+        pair[i] = __floats2bfloat162_rn(xielu_f(v.x, up, down), xielu_f(v.y, up, down));
+    }
+    out[idx] = raw;
+}
+
 }  // namespace
 
 GK_EXPORT int gk_add_layernorm(float* h, const void* delta, int delta_dtype, float delta_scale, const void* weight,
@@ -271,5 +302,27 @@ GK_EXPORT int gk_relu_squared(const void* in, void* out, int dtype, long long to
         gk_launch(relu_squared_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, (const T*)in, (T*)out, total);
     })
     GK_CHECK_LAUNCH("relu_squared");
+    return GK_OK;
+}
+
+GK_EXPORT int gk_xielu(const void* in, void* out, int dtype, long long total, float up, float down, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype), "xielu: bad dtype %d", dtype);
+    GK_REQUIRE(total >= 0, "xielu: bad size");
+    if (total == 0) return GK_OK;
+    const int threads = 256;
+    if (dtype == GK_BF16 && total % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+        const long long pieces = total / 8, blocks8 = (pieces + threads - 1) / threads;
+        GK_REQUIRE(blocks8 < 2147483647LL, "xielu: too many elements");
+        gk_launch(xielu_bf16x8_kernel, dim3((unsigned)blocks8), dim3(threads), 0, (cudaStream_t)stream, (const uint4*)in, (uint4*)out,
+                  pieces, up, down);
+        GK_CHECK_LAUNCH("xielu");
+        return GK_OK;
+    }
+    const long long blocks = (total + threads - 1) / threads;
+    GK_REQUIRE(blocks < 2147483647LL, "xielu: too many elements");
+    GK_DISPATCH_DTYPE(dtype, T, {
+        gk_launch(xielu_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, (cudaStream_t)stream, (const T*)in, (T*)out, total, up, down);
+    })
+    GK_CHECK_LAUNCH("xielu");
     return GK_OK;
 }

@@ -3,7 +3,9 @@
 //   heads_prepare:  a warp per (token, head) of the packed projection q | k | v: optional SiLU (on q and k, on v),
 //                   rotation by position of the first `rot` entries of a q or k head (entry i paired with i + rot/2;
 //                   cosines and sines from tables of rot/2 angles a position), then optional division of a q or k
-//                   head by its root mean square (eps inside the root, no weight), then a constant on k.  The results
+//                   head by its root mean square (eps inside the root, no weight), then a constant on k.  With flag 8
+//                   every value head turns by its own position over ALL of its dv entries (entry m paired with
+//                   m + dv/2, tables of dv/2 angles a position of their own), so that it is cached turned.  The results
 //                   go either to 32-bit arrays q, k [T, heads, d] and v [T, heads, dv] (what a recurrence reads), or
 //                   q to an array of the run's type and k, v into the pages of the cache (what attention reads).
 //   decay_scan:     per (sequence, head):  S <- decay_h S + k_t v_t^T ;  o_t = S^T q_t,  S [d, dv] 32-bit, read from
@@ -24,12 +26,12 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); 
 constexpr int PREP_WARPS = 8;
 constexpr int PREP_MAX = 16;  // heads of up to 512 entries
 
-// flags: 1 SiLU on q and k, 2 SiLU on v, 4 unit root mean square of q and k
+// flags: 1 SiLU on q and k, 2 SiLU on v, 4 unit root mean square of q and k, 8 values turned by position
 template <typename T, typename TQ>
 __global__ void __launch_bounds__(PREP_WARPS * 32) heads_prepare_kernel(
     const T* __restrict__ proj, long long ld, int q_at, int k_at, int v_at, int n_q, int n_k, int d, int dv, int flags,
-    int rot, const float* __restrict__ cos_t, const float* __restrict__ sin_t, float unit_eps, float k_scale,
-    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+    int rot, const float* __restrict__ cos_t, const float* __restrict__ sin_t, const float* __restrict__ v_cos,
+    const float* __restrict__ v_sin, float unit_eps, float k_scale, const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
     TQ* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ v_out, T* __restrict__ k_pages,
     T* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages, int page_size, int write_kv, long long n_items) {
     extern __shared__ float stage[];  // PREP_WARPS * max(d, dv)
@@ -90,6 +92,24 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) heads_prepare_kernel(
         if (kind == 1 && k_scale != 1.f) {
 #pragma unroll
             for (int c = 0; c < PREP_MAX; ++c) x[c] *= k_scale;
+        }
+    }
+    if (kind == 2 && (flags & 8)) {
+        float* mine = stage + (size_t)warp * (d > dv ? d : dv);
+#pragma unroll
+        for (int c = 0; c < PREP_MAX; ++c) {
+            const int i = lane + 32 * c;
+            if (i < width) mine[i] = x[c];
+        }
+        __syncwarp();
+        const int half = dv >> 1;
+        const float* cs = v_cos + (size_t)pos * half;
+        const float* sn = v_sin + (size_t)pos * half;
+#pragma unroll
+        for (int c = 0; c < PREP_MAX; ++c) {
+            const int i = lane + 32 * c;
+            if (i < half) x[c] = mine[i] * cs[i] - mine[i + half] * sn[i];
+            else if (i < 2 * half) x[c] = mine[i] * cs[i - half] + mine[i - half] * sn[i - half];
         }
     }
     if (kind == 0) {
@@ -289,8 +309,8 @@ __global__ void __launch_bounds__(256) group_norm_gate_wide_kernel(const float* 
 }  // namespace
 
 GK_EXPORT int gk_heads_prepare(const void* proj, int dtype, long long ld, int q_at, int k_at, int v_at, int n_q, int n_k, int d,
-                               int dv, int flags, int rot, const float* cos_t, const float* sin_t, float unit_eps, float k_scale,
-                               const int* tok_pos, const int* tok_seq, const int* slots, void* q_out, int q_dtype, float* k_out,
+                               int dv, int flags, int rot, const float* cos_t, const float* sin_t, const float* v_cos,
+                               const float* v_sin, float unit_eps, float k_scale, const int* tok_pos, const int* tok_seq, const int* slots, void* q_out, int q_dtype, float* k_out,
                                float* v_out, void* k_pages, void* v_pages, const int* block_table, int max_pages, int page_size,
                                int write_kv, int n_tokens, void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(q_dtype), "heads_prepare: bad dtype");
@@ -299,6 +319,8 @@ GK_EXPORT int gk_heads_prepare(const void* proj, int dtype, long long ld, int q_
     GK_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, "heads_prepare: %d rotated entries in heads of %d", rot, d);
     GK_REQUIRE(rot == 0 || (cos_t != nullptr && sin_t != nullptr), "heads_prepare: a rotation needs its tables");
     GK_REQUIRE(!(flags & 4) || unit_eps > 0.f, "heads_prepare: eps must be positive");
+    GK_REQUIRE(!(flags & 8) || (v_cos != nullptr && v_sin != nullptr && dv % 2 == 0),
+               "heads_prepare: turned values need their tables and an even size");
     const bool to_pages = k_pages != nullptr;
     GK_REQUIRE(to_pages ? (v_pages != nullptr && block_table != nullptr && page_size > 0 && q_dtype == dtype)
                         : (k_out != nullptr && v_out != nullptr && q_dtype == GK_F32),
@@ -312,11 +334,11 @@ GK_EXPORT int gk_heads_prepare(const void* proj, int dtype, long long ld, int q_
     GK_DISPATCH_DTYPE(dtype, T, {
         if (to_pages) {
             gk_launch(heads_prepare_kernel<T, T>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), smem, s, (const T*)proj, ld, q_at,
-                      k_at, v_at, n_q, n_k, d, dv, flags, rot, cos_t, sin_t, unit_eps, k_scale, tok_pos, tok_seq, slots, (T*)q_out,
+                      k_at, v_at, n_q, n_k, d, dv, flags, rot, cos_t, sin_t, v_cos, v_sin, unit_eps, k_scale, tok_pos, tok_seq, slots, (T*)q_out,
                       (float*)nullptr, (float*)nullptr, (T*)k_pages, (T*)v_pages, block_table, max_pages, page_size, write_kv, items);
         } else {
             gk_launch(heads_prepare_kernel<T, float>, dim3((unsigned)blocks), dim3(PREP_WARPS * 32), smem, s, (const T*)proj, ld,
-                      q_at, k_at, v_at, n_q, n_k, d, dv, flags, rot, cos_t, sin_t, unit_eps, k_scale, tok_pos, tok_seq, slots,
+                      q_at, k_at, v_at, n_q, n_k, d, dv, flags, rot, cos_t, sin_t, v_cos, v_sin, unit_eps, k_scale, tok_pos, tok_seq, slots,
                       (float*)q_out, k_out, v_out, (T*)nullptr, (T*)nullptr, block_table, max_pages, page_size, write_kv, items);
         }
     })

@@ -5,6 +5,8 @@
 //                two largest choice scores and only the experts of the best `keep` groups may be chosen.  The `top`
 //                largest choice scores among them are chosen (ties: the lower index); a chosen expert's weight is its s
 //                (without the correction) times a constant.
+//                With `logits` = 1 the score is the logit itself plus a stored bias, s = z + b (no sigmoid, choice by s),
+//                and the chosen experts' weights are the softmax over the chosen scores alone, times the constant.
 //   experts_up   act[pair] = silu(W_gate[e] h_t) * (W_up[e] h_t) for every pair (token, chosen expert)
 //   experts_down out_t = add_t + sum over the token's pairs, in the order they were chosen, of weight * W_down[e] act[pair]
 //                (32-bit result: it is what goes into the residual stream)
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_scores_kernel(const T*
 // The choice from the scores: one warp per token.
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_choose_kernel(
     const float* __restrict__ z, const float* __restrict__ correction, int* __restrict__ ids, float* __restrict__ weights,
-    int n_tokens, int n_experts, int top, int n_groups, int keep, float scale) {
+    int n_tokens, int n_experts, int top, int n_groups, int keep, float scale, int logits) {
     extern __shared__ float route_smem[];  // per warp: s [E] | choice [E] | group score [n_groups]
     pdl_launch_dependents();
     pdl_wait();
@@ -79,9 +81,10 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_choose_kernel(
     float* choice = s + n_experts;
     float* group_score = choice + n_experts;
     for (int e = lane; e < n_experts; e += 32) {
-        const float sg = 1.f / (1.f + expf(-z[(size_t)t * n_experts + e]));
+        const float ze = z[(size_t)t * n_experts + e];
+        const float sg = logits ? ze + correction[e] : 1.f / (1.f + expf(-ze));
         s[e] = sg;
-        choice[e] = sg + correction[e];
+        choice[e] = logits ? sg : sg + correction[e];
     }
     __syncwarp();
     const int per = n_experts / n_groups;
@@ -122,10 +125,18 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_choose_kernel(
         if (arg == 0x7fffffff) arg = 0;  // nothing left to choose from: cannot happen when top <= allowed experts
         if (lane == 0) {
             ids[(size_t)t * top + pick] = arg;
-            weights[(size_t)t * top + pick] = s[arg] * scale;
+            weights[(size_t)t * top + pick] = logits ? s[arg] : s[arg] * scale;
             choice[arg] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (logits && lane == 0) {
+        // softmax over the chosen scores, in the order they were chosen (the first is the largest)
+        float* w = weights + (size_t)t * top;
+        const float largest = w[0];
+        float sum = 0.f;
+        for (int pick = 0; pick < top; ++pick) sum += expf(w[pick] - largest);
+        for (int pick = 0; pick < top; ++pick) w[pick] = expf(w[pick] - largest) / sum * scale;
     }
 }
 
@@ -376,7 +387,8 @@ GK_EXPORT int gk_experts_combine(const void* y, int dtype, const int* place_of, 
 }
 
 GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, const float* correction, float* z, int* ids,
-                              float* weights, int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale, void* stream) {
+                              float* weights, int n_tokens, int width, int n_experts, int top, int n_groups, int keep, float scale, int logits,
+                              void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype), "route_groups: bad dtype %d", dtype);
     GK_REQUIRE(n_experts > 0 && top > 0 && top <= n_experts, "route_groups: %d of %d experts", top, n_experts);
     GK_REQUIRE(n_groups >= 1 && n_experts % n_groups == 0 && keep >= 1 && keep <= n_groups, "route_groups: %d groups, %d kept, %d experts",
@@ -401,7 +413,7 @@ GK_EXPORT int gk_route_groups(const void* h, int dtype, const float* w_router, c
     })
     GK_CHECK_LAUNCH("route_scores");
     gk_launch(route_choose_kernel, dim3((n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32), smem, s, (const float*)z,
-              correction, ids, weights, n_tokens, n_experts, top, n_groups, keep, scale);
+              correction, ids, weights, n_tokens, n_experts, top, n_groups, keep, scale, logits);
     GK_CHECK_LAUNCH("route_groups");
     return GK_OK;
 }

@@ -6,6 +6,8 @@
 //   merge:   v   = x + scale * (y / sqrt(mean(y^2) + eps_y)) * w_y          (w_y holds the effective weights)
 //            kept[n] = v ;  v = sum_{j <= n} mix[j] * kept[j]               (if a history is given)
 //            x_out = v ;  z = (v / sqrt(mean(v^2) + eps_z)) * w_z           (if a next norm is given)
+//                         z = v in z's type                                 (if z is given without weights: the next
+//                                                                            sublayer reads the stream itself)
 //   conv:    g_t = a_t + sum_j w[j, :] * a_(t - taps + 1 + j)  (weights [taps, width]), a before the sequence's start = 0, a before the
 //            step's start read from the sequence's state (its last taps - 1 inputs)
 //   state:   after the step the state holds the sequence's last taps - 1 inputs
@@ -52,6 +54,10 @@ __global__ void __launch_bounds__(ROW_THREADS) branch_merge_kernel(
         ss2 = fmaf(v, v, ss2);
     }
     if (z == nullptr) return;
+    if (w_z == nullptr) {  // each thread reads back what it wrote itself
+        for (int i = threadIdx.x; i < width; i += ROW_THREADS) z[at + i] = from_float<TZ>(row[i]);
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float r2 = 1.f / sqrtf(ss2 / (float)width + eps_z);
     for (int i = threadIdx.x; i < width; i += ROW_THREADS) z[at + i] = from_float<TZ>(row[i] * r2 * w_z[i]);
@@ -133,6 +139,10 @@ __global__ void __launch_bounds__(ROW_THREADS) branch_merge_x4_kernel(
         for (int e = 0; e < 4; ++e) ss2 = fmaf(v[e], v[e], ss2);
     }
     if (z == nullptr) return;
+    if (w_z == nullptr) {  // each thread reads back what it wrote itself
+        for (int i = threadIdx.x * 4; i < width; i += ROW_THREADS * 4) store_x4<TZ>(z + at + i, *reinterpret_cast<const float4*>(row + i));
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float r2 = 1.f / sqrtf(ss2 / (float)width + eps_z);
     for (int i = threadIdx.x * 4; i < width; i += ROW_THREADS * 4) {
@@ -279,7 +289,28 @@ __global__ void gelu_tanh_bf16x8_kernel(const uint4* __restrict__ in, uint4* __r
     out[idx] = raw;
 }
 
+// The 32-bit stream in another type, element by element (what a sublayer that reads the stream itself multiplies).
+template <typename T>
+__global__ void stream_cast_kernel(const float* __restrict__ x, T* __restrict__ out, long long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) out[idx] = from_float<T>(x[idx]);
+}
+
 }  // namespace
+
+GK_EXPORT int gk_stream_cast(const float* x, void* out, int out_dtype, long long total, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(out_dtype) && total >= 0, "stream_cast: bad arguments");
+    if (total == 0) return GK_OK;
+    const long long blocks = (total + 255) / 256;
+    GK_REQUIRE(blocks < 2147483647LL, "stream_cast: too many elements");
+    GK_DISPATCH_DTYPE(out_dtype, T, {
+        gk_launch(stream_cast_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, (T*)out, total);
+    })
+    GK_CHECK_LAUNCH("stream_cast");
+    return GK_OK;
+}
 
 GK_EXPORT int gk_branch_merge(const float* x, const void* y, int y_dtype, const float* w_y, const float* scale, float eps_y,
                               float* kept, long long kept_stride, int n_kept, const float* mix, float* x_out,
@@ -287,9 +318,9 @@ GK_EXPORT int gk_branch_merge(const float* x, const void* y, int y_dtype, const 
     GK_REQUIRE(GK_VALID_DTYPE(y_dtype) && GK_VALID_DTYPE(z_dtype), "branch_merge: bad dtype code");
     GK_REQUIRE(n_rows >= 0 && width > 0, "branch_merge: bad sizes rows=%d width=%d", n_rows, width);
     GK_REQUIRE(x && y && w_y && x_out, "branch_merge: the stream, the branch and its norm weights are needed");
-    GK_REQUIRE(eps_y > 0.f && (z == nullptr || eps_z > 0.f), "branch_merge: eps must be positive");
+    GK_REQUIRE(eps_y > 0.f && (w_z == nullptr || eps_z > 0.f), "branch_merge: eps must be positive");
     GK_REQUIRE((kept == nullptr) == (mix == nullptr) && n_kept >= 0, "branch_merge: a history needs mixing weights");
-    GK_REQUIRE((z == nullptr) == (w_z == nullptr), "branch_merge: a next norm needs weights and an output");
+    GK_REQUIRE(w_z == nullptr || z != nullptr, "branch_merge: a next norm needs an output");
     const size_t smem = (size_t)width * sizeof(float);
     GK_REQUIRE(smem <= 200 * 1024, "branch_merge: rows of %d do not fit in shared memory", width);
     if (n_rows == 0) return GK_OK;

@@ -6,8 +6,15 @@
 //                          position (entry i paired with i + rot/2; cos and sin from tables [positions, rot/2]) and the
 //                          rest pass; the finished key goes into the key pages and the key AS PROJECTED (before norm
 //                          and rotation) into the value pages.  One block per token, 32-bit arithmetic.
+//                          With v_at >= 0 the values are a projection of their own (n_kv heads of dv entries from
+//                          column v_at of the row) and go into the value pages as projected; with has_k = 0 the row
+//                          holds queries only (a layer that reads another layer's keys and values).
 //   sigmoid_gate           out = o * sigmoid(gate), the gate read from a column range of a wider row
 //   softcap                x <- cap * tanh(x / cap), in place (32-bit logits)
+//   turn_back_gate         every head's read-out o [dv] turned by MINUS the reading token's position over all of its
+//                          entries (entry m paired with m + dv/2; what undoes, for the sum over keys, a turn of every
+//                          value by its own position), then times sigmoid of ONE number per head, read from a column
+//                          range of a wider row.  Either half may be left out.
 
 #include "common.cuh"
 
@@ -21,19 +28,19 @@ __global__ void __launch_bounds__(WN_THREADS) wide_norm_rope_write_kernel(
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ tok_pos,
     const int* __restrict__ tok_seq, const int* __restrict__ slots, const int* __restrict__ block_table,
     T* __restrict__ q_out, TC* __restrict__ k_pages, TC* __restrict__ v_pages, int n_q, int n_kv, int d, int rot,
-    int max_pages, int page_size, float eps) {
+    int max_pages, int page_size, float eps, int v_at, int dv, int has_k) {
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const T* row = proj + (size_t)t * ld;
-    const int nq = n_q * d, nk = n_kv * d;
+    const int nq = n_q * d, nk = has_k ? n_kv * d : 0;
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x; i < nq; i += WN_THREADS) { const float v = to_float(row[i]); sq = fmaf(v, v, sq); }
     for (int i = threadIdx.x; i < nk; i += WN_THREADS) { const float v = to_float(row[nq + i]); sk = fmaf(v, v, sk); }
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
-    const float rq = 1.f / sqrtf(sq / (float)nq + eps), rk = 1.f / sqrtf(sk / (float)nk + eps);
+    const float rq = 1.f / sqrtf(sq / (float)nq + eps), rk = nk ? 1.f / sqrtf(sk / (float)nk + eps) : 0.f;
     const int pos = tok_pos[t];
     const int half = rot >> 1;
     const float* cs = cos_t + (size_t)pos * half;
@@ -60,7 +67,14 @@ __global__ void __launch_bounds__(WN_THREADS) wide_norm_rope_write_kernel(
             const int page = block_table[(size_t)slots[tok_seq[t]] * max_pages + pos / page_size];
             const size_t dst = (((size_t)page * n_kv + hk) * page_size + pos % page_size) * d + j;
             k_pages[dst] = from_float<TC>(res);
-            v_pages[dst] = from_float<TC>(to_float(row[i]));
+            if (v_at < 0) v_pages[dst] = from_float<TC>(to_float(row[i]));
+        }
+    }
+    if (v_at >= 0 && nk && k_pages != nullptr) {
+        const int page = block_table[(size_t)slots[tok_seq[t]] * max_pages + pos / page_size];
+        for (int i = threadIdx.x; i < n_kv * dv; i += WN_THREADS) {
+            const int hk = i / dv, j = i - hk * dv;
+            v_pages[(((size_t)page * n_kv + hk) * page_size + pos % page_size) * dv + j] = from_float<TC>(to_float(row[v_at + i]));
         }
     }
 }
@@ -85,15 +99,69 @@ __global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
     if (i < n) x[i] = cap * tanhf(x[i] / cap);
 }
 
+// One thread per (token, head, pair of entries).
+template <typename T>
+__global__ void turn_back_gate_kernel(const T* __restrict__ o, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                      const int* __restrict__ tok_pos, const T* __restrict__ gate, long long ld_gate,
+                                      T* __restrict__ out, long long n, int n_heads, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int half = dv >> 1;
+    const long long th = i / half;
+    const int m = (int)(i - th * half);
+    const long long t = th / n_heads;
+    const int h = (int)(th - t * n_heads);
+    const size_t at = (size_t)th * dv;
+    float a = to_float(o[at + m]), b = to_float(o[at + m + half]);
+    if (cos_t != nullptr) {
+        const size_t row = (size_t)tok_pos[t] * half + m;
+        const float c = cos_t[row], s = sin_t[row];
+        const float ra = a * c + b * s, rb = b * c - a * s;  // the turn by minus the angle
+        a = ra;
+        b = rb;
+    }
+    if (gate != nullptr) {
+        const float g = 1.f / (1.f + expf(-to_float(gate[t * ld_gate + h])));
+        a *= g;
+        b *= g;
+    }
+    out[at + m] = from_float<T>(a);
+    out[at + m + half] = from_float<T>(b);
+}
+
 }  // namespace
+
+GK_EXPORT int gk_turn_back_gate(const void* o, const float* cos_t, const float* sin_t, int table_positions, int max_position,
+                                const int* tok_pos, const void* gate, long long ld_gate, void* out, int dtype, long long n_tokens,
+                                int n_heads, int dv, void* stream) {
+    GK_REQUIRE(GK_VALID_DTYPE(dtype) && n_heads > 0 && dv > 0 && dv % 2 == 0, "turn_back_gate: bad arguments");
+    GK_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "turn_back_gate: a turn needs both tables");
+    GK_REQUIRE(cos_t == nullptr || (tok_pos != nullptr && max_position < table_positions),
+               "turn_back_gate: position %d is beyond the tables (%d)", max_position, table_positions);
+    if (n_tokens == 0) return GK_OK;
+    const long long n = n_tokens * n_heads * (dv / 2);
+    const long long blocks = (n + 255) / 256;
+    GK_REQUIRE(blocks < 2147483647LL, "turn_back_gate: too many elements");
+    GK_DISPATCH_DTYPE(dtype, T, {
+        gk_launch(turn_back_gate_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const T*)o, cos_t, sin_t, tok_pos,
+                  (const T*)gate, ld_gate, (T*)out, n, n_heads, dv);
+    })
+    GK_CHECK_LAUNCH("turn_back_gate");
+    return GK_OK;
+}
 
 GK_EXPORT int gk_wide_norm_rope_write(const void* proj, int dtype, long long ld, const float* w_q, const float* w_k,
                                       const float* cos_t, const float* sin_t, int table_positions, const int* tok_pos,
                                       const int* tok_seq, const int* slots, const int* block_table, void* q_out, void* k_pages,
                                       void* v_pages, int cache_dtype, int n_tokens, int n_q, int n_kv, int d, int rot,
-                                      int max_pages, int page_size, float eps, int max_position, void* stream) {
+                                      int max_pages, int page_size, float eps, int max_position, int v_at, int dv, int has_k,
+                                      void* stream) {
     GK_REQUIRE(GK_VALID_DTYPE(dtype) && GK_VALID_DTYPE(cache_dtype), "wide_norm_rope_write: bad dtype");
     GK_REQUIRE(n_q > 0 && n_kv > 0 && d > 0, "wide_norm_rope_write: bad sizes");
+    GK_REQUIRE(v_at < 0 || dv > 0, "wide_norm_rope_write: values of their own need a size");
+    GK_REQUIRE(has_k || k_pages == nullptr, "wide_norm_rope_write: a row without keys writes no pages");
     GK_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, "wide_norm_rope_write: %d rotated entries in heads of %d", rot, d);
     GK_REQUIRE(rot == 0 || (cos_t != nullptr && sin_t != nullptr && max_position < table_positions),
                "wide_norm_rope_write: position %d is beyond the rotation tables (%d)", max_position, table_positions);
@@ -103,7 +171,7 @@ GK_EXPORT int gk_wide_norm_rope_write(const void* proj, int dtype, long long ld,
         GK_DISPATCH_DTYPE(cache_dtype, TC, {
             gk_launch(wide_norm_rope_write_kernel<T, TC>, dim3(n_tokens), dim3(WN_THREADS), 0, s, (const T*)proj, ld, w_q, w_k, cos_t,
                       sin_t, tok_pos, tok_seq, slots, block_table, (T*)q_out, (TC*)k_pages, (TC*)v_pages, n_q, n_kv, d, rot, max_pages,
-                      page_size, eps);
+                      page_size, eps, v_at, dv, has_k);
         })
     })
     GK_CHECK_LAUNCH("wide_norm_rope_write");

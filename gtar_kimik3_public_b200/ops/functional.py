@@ -1050,11 +1050,12 @@ class PagedRows:
 def branch_merge(x: torch.Tensor, y: torch.Tensor, norm_weight: torch.Tensor, eps: float, scale: torch.Tensor | None = None,
                  kept: torch.Tensor | None = None, n_kept: int = 0, mix: torch.Tensor | None = None,
                  next_weight: torch.Tensor | None = None, next_eps: float = 0.0, next_dtype: torch.dtype = torch.float32,
-                 x_out: torch.Tensor | None = None):
+                 x_out: torch.Tensor | None = None, copy_dtype: torch.dtype | None = None):
     """``v = x + scale * rmsnorm(y) * norm_weight``; with ``kept`` ``[n, rows, width]``: ``kept[n_kept] = v`` and
     ``v = sum_{j <= n_kept} mix[j] * kept[j]``; the new stream goes to ``x_out`` (default: ``x`` itself); with
-    ``next_weight`` also returns ``rmsnorm(v) * next_weight`` in ``next_dtype``.  All weights are 32-bit effective
-    weights.  Returns ``(stream, normed or None)``."""
+    ``next_weight`` also returns ``rmsnorm(v) * next_weight`` in ``next_dtype``; with ``copy_dtype`` instead, the new
+    stream itself in that type (for a sublayer that reads the stream without a norm).  All weights are 32-bit effective
+    weights.  Returns ``(stream, normed or copy or None)``."""
     require_device(x.device)
     _check(x, "x", torch.float32, 2)
     _check(y, "y", dims=2)
@@ -1080,6 +1081,9 @@ def branch_merge(x: torch.Tensor, y: torch.Tensor, norm_weight: torch.Tensor, ep
     z = None
     if next_weight is not None:
         z = torch.empty((rows, width), dtype=next_dtype, device=x.device)
+    elif copy_dtype is not None:
+        next_dtype = copy_dtype
+        z = torch.empty((rows, width), dtype=copy_dtype, device=x.device)
     call("gk_branch_merge", ptr(x), ptr(y), dtype_code(y.dtype), ptr(norm_weight), ptr(scale), float(eps), ptr(kept), stride,
          int(n_kept), ptr(mix), ptr(x_out), ptr(next_weight), float(next_eps), ptr(z), dtype_code(next_dtype), rows, width,
          stream_ptr())
@@ -1344,9 +1348,11 @@ def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, ga
 
 # ------------------------------------------------------------------ routed experts
 def route_groups(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, top: int, n_groups: int, keep: int,
-                 scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+                 scale: float, logits: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """Chosen experts ``[T, top]`` (int32) and their weights (float32): sigmoid scores, choice by score plus
-    ``correction`` among the experts of the best ``keep`` of ``n_groups`` groups, weight = score times ``scale``."""
+    ``correction`` among the experts of the best ``keep`` of ``n_groups`` groups, weight = score times ``scale``.
+    ``logits``: the score is the logit plus ``correction`` (a bias), the choice goes by it, and the weights are the
+    softmax over the chosen scores alone, times ``scale``."""
     require_device(h.device)
     _check(h, "h", dims=2)
     _check(w_router, "w_router", torch.float32, 2)
@@ -1359,7 +1365,7 @@ def route_groups(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tens
     weights = torch.empty((T, top), dtype=torch.float32, device=h.device)
     z = torch.empty((T, n_experts), dtype=torch.float32, device=h.device)
     call("gk_route_groups", ptr(h), dtype_code(h.dtype), ptr(w_router), ptr(correction), ptr(z), ptr(ids), ptr(weights), T, width, n_experts,
-         top, n_groups, keep, float(scale), stream_ptr())
+         top, n_groups, keep, float(scale), int(bool(logits)), stream_ptr())
     return ids, weights
 
 
@@ -1392,19 +1398,27 @@ def experts_pairwise(h: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Ten
 # ------------------------------------------------------------------ attention with norms over whole projections
 def wide_norm_rope_write(proj: torch.Tensor, n_q: int, n_kv: int, d: int, w_q: torch.Tensor, w_k: torch.Tensor, eps: float,
                          cos: torch.Tensor | None, sin: torch.Tensor | None, rot: int, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
-                         slots: torch.Tensor, kv: PagedKV, max_position: int, write_kv: bool = True) -> torch.Tensor:
+                         slots: torch.Tensor, kv: PagedKV, max_position: int, write_kv: bool = True, v_at: int | None = None,
+                         has_k: bool = True) -> torch.Tensor:
     """RMS norm of the whole query row and of the whole key row of every token (``proj [T, >= (n_q + n_kv) d]`` holds
     q | k), rotation of the first ``rot`` entries of every head, the finished keys into the key pages and the keys as
-    projected into the value pages.  Returns the finished queries ``[T, n_q, d]``."""
+    projected into the value pages.  With ``v_at`` the values are a projection of their own, from that column of the
+    row on, as wide as the value pages say.  ``has_k`` False: the row holds queries only and nothing is written (a
+    layer that reads another layer's pages).  Returns the finished queries ``[T, n_q, d]``."""
     require_device(proj.device)
     _check(proj, "proj", dims=2)
     _check(w_q, "w_q", torch.float32, 1)
     _check(w_k, "w_k", torch.float32, 1)
     T = proj.shape[0]
-    if proj.shape[1] < (n_q + n_kv) * d or w_q.shape[0] != n_q * d or w_k.shape[0] != n_kv * d:
+    dv = kv.v.shape[3]
+    if not has_k:
+        write_kv, v_at = False, None
+    if proj.shape[1] < (n_q + (n_kv if has_k else 0)) * d or w_q.shape[0] != n_q * d or (has_k and w_k.shape[0] != n_kv * d):
         raise KernelError("wide_norm_rope_write: sizes do not fit")
-    if kv.k.shape[1] != n_kv or kv.k.shape[3] != d or kv.v.shape != kv.k.shape:
-        raise KernelError(f"pages {tuple(kv.k.shape)} do not fit n_kv={n_kv}, head_dim={d}")
+    if v_at is not None and (v_at < (n_q + n_kv) * d or proj.shape[1] < v_at + n_kv * dv):
+        raise KernelError("wide_norm_rope_write: the values do not lie behind the keys inside the row")
+    if kv.k.shape[1] != n_kv or kv.k.shape[3] != d or (has_k and v_at is None and kv.v.shape != kv.k.shape) or kv.v.shape[:3] != kv.k.shape[:3]:
+        raise KernelError(f"pages {tuple(kv.k.shape)} / {tuple(kv.v.shape)} do not fit n_kv={n_kv}, head_dim={d}")
     positions = 0
     if rot:
         _check(cos, "cos", torch.float32, 2)
@@ -1416,8 +1430,57 @@ def wide_norm_rope_write(proj: torch.Tensor, n_q: int, n_kv: int, d: int, w_q: t
     call("gk_wide_norm_rope_write", ptr(proj), dtype_code(proj.dtype), proj.shape[1], ptr(w_q), ptr(w_k), ptr(cos) if rot else None,
          ptr(sin) if rot else None, positions, ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(kv.block_table), ptr(q),
          ptr(kv.k) if write_kv else None, ptr(kv.v) if write_kv else None, dtype_code(kv.k.dtype), T, n_q, n_kv, d, int(rot),
-         kv.max_pages, kv.page_size, float(eps), int(max_position), stream_ptr())
+         kv.max_pages, kv.page_size, float(eps), int(max_position), -1 if v_at is None else int(v_at), int(dv), int(bool(has_k)),
+         stream_ptr())
     return q
+
+
+def turn_back_gate(o: torch.Tensor, cos: torch.Tensor | None, sin: torch.Tensor | None, tok_pos: torch.Tensor, max_position: int,
+                   gate: torch.Tensor | None = None, gate_at: int = 0) -> torch.Tensor:
+    """Every head's read-out ``o [T, n_heads, dv]`` turned by minus its token's position over all ``dv`` entries (entry
+    ``m`` paired with ``m + dv/2``; ``cos``, ``sin`` ``[positions, dv/2]``; None: no turn), then times the sigmoid of one
+    number per head, ``gate[:, gate_at + h]`` (None: no gate)."""
+    require_device(o.device)
+    _check(o, "o", dims=3)
+    T, n_heads, dv = o.shape
+    positions = 0
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        _check(tok_pos, "tok_pos", torch.int32, 1)
+        if cos.shape[1] != dv // 2 or sin.shape != cos.shape or dv % 2:
+            raise KernelError(f"turn_back_gate: tables of {cos.shape[1]} angles for read-outs of {dv}")
+        positions = cos.shape[0]
+    gate_ptr, ld = None, 0
+    if gate is not None:
+        _check(gate, "gate", o.dtype, 2)
+        if gate.shape[0] != T or gate.shape[1] < gate_at + n_heads:
+            raise KernelError("turn_back_gate: the gate is narrower than the heads")
+        gate_ptr, ld = gate.data_ptr() + gate_at * gate.element_size(), gate.shape[1]
+    out = torch.empty_like(o)
+    call("gk_turn_back_gate", ptr(o), ptr(cos), ptr(sin), positions, int(max_position), ptr(tok_pos), gate_ptr, ld, ptr(out),
+         dtype_code(o.dtype), T, n_heads, dv, stream_ptr())
+    return out
+
+
+def xielu(x: torch.Tensor, up: float, down: float) -> torch.Tensor:
+    """``up z^2 + z/2`` above zero, ``down (exp(z) - 1 - z) + z/2`` at and below, element by element (32-bit arithmetic)."""
+    require_device(x.device)
+    _check(x, "x")
+    out = torch.empty_like(x)
+    call("gk_xielu", ptr(x), ptr(out), dtype_code(x.dtype), x.numel(), float(up), float(down), stream_ptr())
+    return out
+
+
+def stream_cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The 32-bit stream in the run's type (the stream itself where that is 32-bit)."""
+    _check(x, "x", torch.float32)
+    if dtype == torch.float32:
+        return x
+    require_device(x.device)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    call("gk_stream_cast", ptr(x), ptr(out), dtype_code(dtype), x.numel(), stream_ptr())
+    return out
 
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, gate_at: int) -> torch.Tensor:
@@ -1573,18 +1636,20 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-PREPARE_SILU_QK, PREPARE_SILU_V, PREPARE_UNIT_RMS = 1, 2, 4
+PREPARE_SILU_QK, PREPARE_SILU_V, PREPARE_UNIT_RMS, PREPARE_TURN_V = 1, 2, 4, 8
 
 
 def heads_prepare(proj: torch.Tensor, q_at: int, k_at: int, v_at: int, n_q: int, n_k: int, d: int, dv: int, tok_pos: torch.Tensor,
                   tok_seq: torch.Tensor, slots: torch.Tensor, *, silu_qk: bool = False, silu_v: bool = False, rot: int = 0,
                   cos: torch.Tensor | None = None, sin: torch.Tensor | None = None, unit_eps: float | None = None,
-                  k_scale: float = 1.0, kv: PagedKV | None = None, write_kv: bool = True, max_position: int | None = None):
+                  k_scale: float = 1.0, kv: PagedKV | None = None, write_kv: bool = True, max_position: int | None = None,
+                  v_cos: torch.Tensor | None = None, v_sin: torch.Tensor | None = None):
     """What stands between a packed projection and a mixer's core.  ``proj [T, >= ...]`` holds ``n_q`` query heads of ``d``
     from column ``q_at``, ``n_k`` key heads of ``d`` from ``k_at`` and ``n_k`` value heads of ``dv`` from ``v_at``.  In this
     order: SiLU (``silu_qk`` on q and k, ``silu_v`` on v); rotation of the first ``rot`` entries of every q and k head by
     the token's position (entry ``i`` with ``i + rot/2``; ``cos``, ``sin`` ``[positions, rot/2]``); with ``unit_eps`` every q
-    and k head divided by its root mean square; ``k_scale`` on k.  With ``kv`` the keys and values are written into the
+    and k head divided by its root mean square; ``k_scale`` on k; with ``v_cos``, ``v_sin`` ``[positions, dv/2]`` every
+    value head turned by its token's position over all of its entries (entry ``m`` with ``m + dv/2``).  With ``kv`` the keys and values are written into the
     cache's pages and q ``[T, n_q, d]`` comes back in the projection's type; without, q, k ``[T, n, d]`` and v ``[T, n_k,
     dv]`` come back as 32-bit arrays."""
     require_device(proj.device)
@@ -1602,6 +1667,14 @@ def heads_prepare(proj: torch.Tensor, q_at: int, k_at: int, v_at: int, n_q: int,
         if max_position is not None and cos.shape[0] <= max_position:
             raise KernelError(f"heads_prepare: tables hold {cos.shape[0]} positions, the step reaches {max_position}")
     flags = (PREPARE_SILU_QK if silu_qk else 0) | (PREPARE_SILU_V if silu_v else 0) | (PREPARE_UNIT_RMS if unit_eps is not None else 0)
+    if v_cos is not None:
+        _check(v_cos, "v_cos", torch.float32, 2)
+        _check(v_sin, "v_sin", torch.float32, 2)
+        if dv % 2 or v_cos.shape[1] != dv // 2 or v_sin.shape != v_cos.shape:
+            raise KernelError(f"heads_prepare: tables of {v_cos.shape[1]} angles for values of {dv}")
+        if max_position is not None and v_cos.shape[0] <= max_position:
+            raise KernelError(f"heads_prepare: value tables hold {v_cos.shape[0]} positions, the step reaches {max_position}")
+        flags |= PREPARE_TURN_V
     dev = proj.device
     if kv is not None:
         _check(kv.k, "k pages", proj.dtype, 4)
@@ -1610,16 +1683,16 @@ def heads_prepare(proj: torch.Tensor, q_at: int, k_at: int, v_at: int, n_q: int,
             raise KernelError(f"heads_prepare: pages {tuple(kv.k.shape)} / {tuple(kv.v.shape)} do not hold {n_k} heads of {d} / {dv}")
         q = torch.empty((T, n_q, d), dtype=proj.dtype, device=dev)
         call("gk_heads_prepare", ptr(proj), dtype_code(proj.dtype), proj.shape[1], q_at, k_at, v_at, n_q, n_k, d, dv, flags, rot,
-             ptr(cos) if rot else None, ptr(sin) if rot else None, float(unit_eps or 0.0), float(k_scale), ptr(tok_pos), ptr(tok_seq),
-             ptr(slots), ptr(q), dtype_code(q.dtype), None, None, ptr(kv.k), ptr(kv.v), ptr(kv.block_table), kv.max_pages,
+             ptr(cos) if rot else None, ptr(sin) if rot else None, ptr(v_cos), ptr(v_sin), float(unit_eps or 0.0), float(k_scale),
+             ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(q), dtype_code(q.dtype), None, None, ptr(kv.k), ptr(kv.v), ptr(kv.block_table), kv.max_pages,
              kv.page_size, int(write_kv), T, stream_ptr())
         return q
     q = torch.empty((T, n_q, d), dtype=torch.float32, device=dev)
     k = torch.empty((T, n_k, d), dtype=torch.float32, device=dev)
     v = torch.empty((T, n_k, dv), dtype=torch.float32, device=dev)
     call("gk_heads_prepare", ptr(proj), dtype_code(proj.dtype), proj.shape[1], q_at, k_at, v_at, n_q, n_k, d, dv, flags, rot,
-         ptr(cos) if rot else None, ptr(sin) if rot else None, float(unit_eps or 0.0), float(k_scale), ptr(tok_pos), ptr(tok_seq),
-         ptr(slots), ptr(q), dtype_code(q.dtype), ptr(k), ptr(v), None, None, None, 0, 0, 0, T, stream_ptr())
+         ptr(cos) if rot else None, ptr(sin) if rot else None, ptr(v_cos), ptr(v_sin), float(unit_eps or 0.0), float(k_scale),
+         ptr(tok_pos), ptr(tok_seq), ptr(slots), ptr(q), dtype_code(q.dtype), ptr(k), ptr(v), None, None, None, 0, 0, 0, T, stream_ptr())
     return q, k, v
 
 
@@ -1702,14 +1775,18 @@ def group_norm_gate(x: torch.Tensor, group: int, weight: torch.Tensor | None, ga
 def attention_scored_exact(q: torch.Tensor, kv: PagedKV, tok_pos: torch.Tensor, tok_seq: torch.Tensor, slots: torch.Tensor,
                            scale: float, window: int = 0, keep_first: int = 0, r1: torch.Tensor | None = None,
                            r2: torch.Tensor | None = None, head_bias: torch.Tensor | None = None,
-                           weights: str = "softmax") -> torch.Tensor:
+                           weights: str = "softmax", chunk: int = 0, temp: torch.Tensor | None = None,
+                           dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None) -> torch.Tensor:
     """Causal grouped-query attention of ``q [T, n_q, d]`` over pages of keys ``[.., d]`` and values ``[.., dv]`` (exact
     kernel): a key at ``j`` is seen from ``i`` if ``i - j < window`` or ``j < keep_first``; the score is ``q . k * scale -
     r1_h ln(1 + r2_h (i - j))``; the weights are the softmax over the seen keys, or ``sigmoid(score + head_bias_h)``
-    without a sum that divides.  Returns ``[T, n_q, dv]``."""
+    without a sum that divides.  ``chunk``: only keys of the token's own chunk of that many positions are seen; ``temp``
+    ``[n_q]`` multiplies the product per head; ``dist_bias [n_dist, n_q]`` is added by distance (the last row for
+    every distance beyond); ``sink [n_q]`` joins the softmax's denominator as ``exp(sink_h)``.  Returns ``[T, n_q, dv]``."""
     require_device(q.device)
     _check(q, "q", dims=3)
     n, n_q, d = q.shape
+    _check_score_rules(n_q, temp, dist_bias, sink)
     _check(kv.k, "k pages", q.dtype, 4)
     _check(kv.v, "v pages", q.dtype, 4)
     n_kv, dv = kv.k.shape[1], kv.v.shape[3]
@@ -1725,8 +1802,21 @@ def attention_scored_exact(q: torch.Tensor, kv: PagedKV, tok_pos: torch.Tensor, 
     out = torch.empty((n, n_q, dv), dtype=q.dtype, device=q.device)
     call("gk_attention_scored_exact", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), dtype_code(q.dtype), ptr(tok_pos), ptr(tok_seq),
          ptr(slots), ptr(kv.block_table), n, n_q, n_kv, d, dv, kv.max_pages, kv.page_size, float(scale), int(window),
-         int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), {"softmax": 0, "sigmoid": 1}[weights], stream_ptr())
+         int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), {"softmax": 0, "sigmoid": 1}[weights], int(chunk), ptr(temp),
+         ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], ptr(sink), stream_ptr())
     return out
+
+
+def _check_score_rules(n_q: int, temp, dist_bias, sink) -> None:
+    for name, t in (("temp", temp), ("sink", sink)):
+        if t is not None:
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != n_q:
+                raise KernelError(f"{name} has {t.shape[0]} entries for {n_q} query heads")
+    if dist_bias is not None:
+        _check(dist_bias, "dist_bias", torch.float32, 2)
+        if dist_bias.shape[1] != n_q or dist_bias.shape[0] < 1:
+            raise KernelError(f"a distance table {tuple(dist_bias.shape)} for {n_q} query heads")
 
 
 def scored_attention_parts(n_seqs: int, n_q: int, n_kv: int, max_q_len: int, visible_pages: int, n_sms: int) -> int:
@@ -1746,7 +1836,8 @@ def scored_attention_parts(n_seqs: int, n_q: int, n_kv: int, max_q_len: int, vis
 def attention_scored(q: torch.Tensor, kv: PagedKV, cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, max_q_len: int,
                      scale: float, window: int = 0, keep_first: int = 0, r1: torch.Tensor | None = None,
                      r2: torch.Tensor | None = None, head_bias: torch.Tensor | None = None, weights: str = "softmax",
-                     n_parts: int = 1) -> torch.Tensor:
+                     n_parts: int = 1, chunk: int = 0, temp: torch.Tensor | None = None, dist_bias: torch.Tensor | None = None,
+                     sink: torch.Tensor | None = None) -> torch.Tensor:
     """:func:`attention_scored_exact` on the tensor cores: bfloat16, keys and values of 64 or 128 entries both, pages of 64
     keys.  The new tokens ``q [n_tokens, n_q, d]`` are packed by sequence (``cu_q``), ``kv_len`` counts each sequence's
     cached tokens including them.  ``n_parts`` > 1 cuts every block's keys into that many blocks whose sums a second
@@ -1768,6 +1859,7 @@ def attention_scored(q: torch.Tensor, kv: PagedKV, cu_q: torch.Tensor, kv_len: t
             _check(t, name, torch.float32, 1)
             if t.shape[0] != n_q:
                 raise KernelError(f"{name} has {t.shape[0]} entries for {n_q} query heads")
+    _check_score_rules(n_q, temp, dist_bias, sink)
     sigmoid = {"softmax": 0, "sigmoid": 1}[weights]
     out = torch.empty_like(q)
     part_o = part_ml = None
@@ -1777,5 +1869,6 @@ def attention_scored(q: torch.Tensor, kv: PagedKV, cu_q: torch.Tensor, kv_len: t
             part_ml = torch.empty((n_parts, n, n_q, 2), dtype=torch.float32, device=q.device)
     call("gk_attention_scored_bf16", ptr(q), ptr(kv.k), ptr(kv.v), ptr(out), ptr(part_o), ptr(part_ml), ptr(cu_q), ptr(kv_len),
          ptr(slots), ptr(kv.block_table), n_seqs, int(max_q_len), n, n_q, kv.k.shape[1], d, kv.max_pages, kv.page_size, float(scale),
-         int(window), int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), sigmoid, int(n_parts), stream_ptr())
+         int(window), int(keep_first), ptr(r1), ptr(r2), ptr(head_bias), sigmoid, int(n_parts), int(chunk), ptr(temp),
+         ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0], ptr(sink), stream_ptr())
     return out

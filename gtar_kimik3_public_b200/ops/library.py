@@ -70,13 +70,16 @@ _SIGNATURES: dict[str, list] = {
     "gk_conv_roll": [P, I, L, P, P, P, I, I, I, P],
     "gk_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     "gk_head_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, P],
-    "gk_route_groups": [P, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
+    "gk_route_groups": [P, I, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
     "gk_experts_up": [P, I, P, I, P, P, I, I, I, I, P],
     "gk_experts_down": [P, I, P, I, P, P, P, P, I, I, I, I, P],
     "gk_experts_sort": [P, I, I, P, P, P, P],
     "gk_gather_rows": [P, I, P, P, I, I, I, P],
     "gk_experts_combine": [P, I, P, P, P, P, I, I, I, P],
-    "gk_wide_norm_rope_write": [P, I, L, P, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "gk_wide_norm_rope_write": [P, I, L, P, P, P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, I, I, P],
+    "gk_turn_back_gate": [P, P, P, I, I, P, P, L, P, I, L, I, I, P],
+    "gk_xielu": [P, P, I, L, F, F, P],
+    "gk_stream_cast": [P, P, I, L, P],
     "gk_sigmoid_gate": [P, P, L, P, I, L, I, P],
     "gk_softcap": [P, L, F, P],
     "gk_add_layernorm": [P, P, I, F, P, I, P, I, P, I, I, F, P],
@@ -84,12 +87,12 @@ _SIGNATURES: dict[str, list] = {
     "gk_scaled_sum": [P, F, P, F, I, P, L, P],
     "gk_relu_squared": [P, P, I, L, P],
     "gk_scale": [P, L, F, P],
-    "gk_heads_prepare": [P, I, L, I, I, I, I, I, I, I, I, I, P, P, F, F, P, P, P, P, I, P, P, P, P, P, I, I, I, I, P],
+    "gk_heads_prepare": [P, I, L, I, I, I, I, I, I, I, I, I, P, P, P, P, F, F, P, P, P, P, I, P, P, P, P, P, I, I, I, I, P],
     "gk_decay_scan": [P, P, P, P, P, P, P, P, I, I, I, I, P],
     "gk_decay_scan_chunked": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "gk_group_norm_gate": [P, P, P, I, L, P, I, L, I, I, F, I, P],
-    "gk_attention_scored_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, I, P],
-    "gk_attention_scored_bf16": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, P],
+    "gk_attention_scored_exact": [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, P, P, I, P, P],
+    "gk_attention_scored_bf16": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, P, P, I, I, I, P, P, I, P, P],
 }
 
 

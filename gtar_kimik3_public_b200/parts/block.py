@@ -1,8 +1,8 @@
 """Pre-norm residual block: ``h += mixer(norm_in(h)); h += ffn(norm_post(h))``
 (src/models/transformer.py:47-48).  The adds are fused into the norm that follows them: the
 block hands its last branch output on as ``pending`` instead of adding it itself.  Beside it: the block with
-convolutions over time in front of its sublayers, the block whose branches share one norm, and the block that norms
-every branch on both sides."""
+convolutions over time in front of its sublayers, the block whose branches share one norm, the block that norms
+every branch on both sides, and the block that norms every branch on its way OUT only."""
 
 from __future__ import annotations
 
@@ -373,3 +373,60 @@ class SandwichBlock(Block):
 
 
 register_part("block", "sandwich", SandwichBlock)
+
+
+class OutNormBlock(Block):
+    """A layer whose sublayers read the stream itself and whose results are normed before they are added:
+
+        x += norm_1(mixer(x));   x += norm_2(feed_forward(x))            (the second left out for a layer without feed-forward)
+
+    The stream is 32-bit; what a sublayer multiplies is the stream in the run's type.  The norm of a branch, its add into
+    the stream and the copy that the next sublayer reads are one kernel; the copy for the next LAYER travels in the
+    step's extras, so only the model's first layer forms one by itself."""
+
+    def __init__(self, norm_1: Norm, mixer: Mixer, norm_2: Norm | None, feed_forward: FeedForward | None,
+                 names: dict[str, str] | None = None, first: bool = False):
+        """``first``: the model's first layer, which nothing hands a copy of the stream."""
+        if (feed_forward is None) != (norm_2 is None):
+            raise ValueError("a feed-forward comes with the norm behind it, or not at all")
+        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
+        self.first = bool(first)
+        self.names = {"mixer": "mix.", "feed_forward": "mlp.", **(names or {})}
+
+    def children(self):
+        parts = [("", self.norm_1), (self.names["mixer"], self.mixer)]
+        if self.feed_forward is not None:
+            parts += [("", self.norm_2), (self.names["feed_forward"], self.feed_forward)]
+        return parts
+
+    def tensor_specs(self):
+        return {prefix + name: spec for prefix, part in self.children() for name, spec in part.tensor_specs().items()}
+
+    def load(self, tensors):
+        for prefix, part in self.children():
+            part.load({name: tensors[prefix + name] for name in part.tensor_specs() if prefix + name in tensors})
+        for norm in (self.norm_1, self.norm_2):
+            if norm is not None:
+                norm.weight = norm.weight.float().contiguous()  # the merging kernel multiplies by 32-bit weights
+
+    def weight_bytes(self):
+        return sum(part.weight_bytes() for _, part in self.children())
+
+    def forward(self, h, pending, ctx: StepContext, cache):
+        if pending is not None:
+            raise ValueError("a layer of this kind takes its stream whole: the layer before must not leave a branch unadded")
+        x = ctx.extras.pop("stream_copy", None)
+        if x is None or self.first:
+            x = F.stream_cast(h, ctx.dtype)
+        copy = None if ctx.dtype == torch.float32 else ctx.dtype  # a 32-bit run reads the stream itself
+        branch = self.mixer.forward(x, ctx, cache)
+        _, x = F.branch_merge(h, branch, self.norm_1.weight, self.norm_1.eps, copy_dtype=copy)
+        if self.feed_forward is not None:
+            branch = self.feed_forward.forward(h if x is None else x, ctx)
+            _, x = F.branch_merge(h, branch, self.norm_2.weight, self.norm_2.eps, copy_dtype=copy)
+        if x is not None:
+            ctx.extras["stream_copy"] = x
+        return h, None
+
+
+register_part("block", "out_norm", OutNormBlock)

@@ -9,6 +9,10 @@ chosen; a chosen expert's output is weighted by ``s * route_scale`` (not renorma
 Tensors: ``e<i>.gate``, ``e<i>.up`` ``[ff, hidden]``, ``e<i>.down`` ``[hidden, ff]``, ``router`` ``[experts, hidden]``,
 ``correction`` ``[experts]``; stacked at load into ``[E, 2, ff, hidden]`` and ``[E, hidden, ff]``.
 
+With ``logit_weights`` the router is plainer: scores are the logits plus a stored bias, ``s = z + b`` (the bias tensor's
+name is the builder's, ``bias_name``), the ``top`` largest are chosen, and the chosen experts' weights are the softmax
+over the chosen scores alone (times ``route_scale``).
+
 The result is 32-bit (it goes into the residual stream); ``forward_added`` folds another branch's output into the
 same sum, for blocks whose branches read one norm.
 """
@@ -26,13 +30,14 @@ class RoutedExperts(FeedForward):
     graph_safe = True
 
     def __init__(self, hidden_size: int, expert_size: int, n_experts: int, top: int, route_scale: float = 1.0,
-                 n_groups: int = 1, keep_groups: int = 1):
+                 n_groups: int = 1, keep_groups: int = 1, logit_weights: bool = False, bias_name: str = "correction"):
         self.hidden_size, self.ff, self.n_experts, self.top = int(hidden_size), int(expert_size), int(n_experts), int(top)
         self.route_scale, self.n_groups, self.keep = float(route_scale), int(n_groups), int(keep_groups)
         if self.n_experts % self.n_groups or not 1 <= self.keep <= self.n_groups:
             raise ValueError(f"{self.n_experts} experts do not form {self.n_groups} equal groups of which {self.keep} are kept")
         if not 1 <= self.top <= self.keep * (self.n_experts // self.n_groups):
             raise ValueError(f"{self.top} experts cannot be chosen from {self.keep} groups of {self.n_experts // self.n_groups}")
+        self.logit_weights, self.bias_name = bool(logit_weights), bias_name
         self.w_gate_up = self.w_down = self.w_router = self.correction = None
         # from this many (token, expert) pairs on, a bfloat16 step sorts its pairs by expert and runs each expert's rows
         # through one tensor-core product; below, every pair streams its expert's weights by itself
@@ -46,7 +51,7 @@ class RoutedExperts(FeedForward):
             specs[f"e{e}.up"] = TensorSpec((ff, W))
             specs[f"e{e}.down"] = TensorSpec((W, ff))
         specs["router"] = TensorSpec((self.n_experts, W), init=(0.0, 0.5))
-        specs["correction"] = TensorSpec((self.n_experts,), "vector", init=(0.0, 0.3))
+        specs[self.bias_name] = TensorSpec((self.n_experts,), "vector", init=(0.0, 0.3))
         return specs
 
     def load(self, tensors):
@@ -56,7 +61,7 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = torch.stack([torch.stack([tensors[f"e{e}.gate"].to(kind), tensors[f"e{e}.up"].to(kind)]) for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"].to(kind) for e in range(E)]).contiguous()
         self.w_router = tensors["router"].float().contiguous()
-        self.correction = tensors["correction"].float().contiguous()
+        self.correction = tensors[self.bias_name].float().contiguous()
 
     def weight_bytes(self):
         """What a single token reads: its ``top`` experts and the router."""
@@ -64,7 +69,8 @@ class RoutedExperts(FeedForward):
         return self.top * per_expert + self.w_router.numel() * 4
 
     def route(self, x: torch.Tensor):
-        return F.route_groups(x, self.w_router, self.correction, self.top, self.n_groups, self.keep, self.route_scale)
+        return F.route_groups(x, self.w_router, self.correction, self.top, self.n_groups, self.keep, self.route_scale,
+                              logits=self.logit_weights)
 
     def forward_added(self, x: torch.Tensor, ctx: StepContext, add: torch.Tensor | None) -> torch.Tensor:
         """``add + experts(x)`` as one 32-bit sum (``add``: another branch's output for the same tokens, or None)."""

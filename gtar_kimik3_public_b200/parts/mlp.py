@@ -114,3 +114,41 @@ class ReluSquaredFeedForward(FeedForward):
 
 
 register_part("feed_forward", "relu_squared", ReluSquaredFeedForward)
+
+
+class XieluFeedForward(FeedForward):
+    """``down(act(up(x)))`` with an activation that is quadratic above zero and exponential below, joined smoothly at
+    zero, shaped by two stored numbers ``p`` and ``q`` (tensor ``act`` ``[2]``):
+
+        z > 0:   softplus(p) z^2 + z / 2          z <= 0:   (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+
+    No gate, no biases.  The two constants are formed once at load, in 32-bit; the activation is a kernel of its own
+    behind the product and works in 32-bit on what the product hands on."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, up_name: str = "up", down_name: str = "down", act_name: str = "act"):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.up_name, self.down_name, self.act_name = up_name, down_name, act_name
+        self.w_up = self.w_down = None
+        self.up_const = self.down_const = 0.0
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {self.up_name: TensorSpec((i, h)), self.down_name: TensorSpec((h, i)),
+                self.act_name: TensorSpec((2,), "vector", init=(0.5, 0.4))}
+
+    def load(self, tensors):
+        self.w_up = tensors[self.up_name].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+        p, q = torch.nn.functional.softplus(tensors[self.act_name].float()).tolist()
+        self.up_const, self.down_const = p, 0.5 + q
+
+    def weight_bytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, x, ctx: StepContext) -> torch.Tensor:
+        return linear(F.xielu(linear(x, self.w_up), self.up_const, self.down_const), self.w_down)
+
+
+register_part("feed_forward", "xielu", XieluFeedForward)

@@ -80,3 +80,7 @@ def _ensure_builtin() -> None:
     from .models.rezulorn import build_rezulorn_plan
 
     register_architecture(RezulornConfig.ARCH_NAMES, RezulornConfig, build_rezulorn_plan)
+    from .config.zasorax import ZasoraxConfig
+    from .models.zasorax import build_zasorax_plan
+
+    register_architecture(ZasoraxConfig.ARCH_NAMES, ZasoraxConfig, build_zasorax_plan)
