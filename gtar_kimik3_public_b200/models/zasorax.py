@@ -18,6 +18,8 @@ Tensor names: ``embed``, ``l<i>.norm1``, ``l<i>.mix.*``, ``l<i>.norm2``, ``l<i>.
 
 from __future__ import annotations
 
+import math
+
 from ..config.zasorax import DEFAULT_BIAS_ROWS, ZasoraxConfig
 from ..parts.base import build_part
 from ..parts.embedding import OutputHead, TokenEmbedding
@@ -51,7 +53,8 @@ def build_zasorax_plan(config: ZasoraxConfig) -> ModelPlan:
         common = dict(hidden_size=width, n_q_heads=m["heads"], n_kv_heads=m["kv_heads"], key_dim=m["dim"], value_dim=m["vdim"],
                       scale=m["scale"], norm_eps=eps, own_kv=source is None)
         if spec["type"] == "attention":
-            rows = m.get("bias_rows") or DEFAULT_BIAS_ROWS  # a model file's tensor has the last word
+            # what the random-weights mode writes (half the rows must lie below bias_max); a model file's tensor has the last word
+            rows = m.get("bias_rows") or max(2, min(DEFAULT_BIAS_ROWS, 2 * (math.ceil(m["bias_max"]) - 1)))
             span = max(r["mask"]["size"] for r in readers[i if source is None else source])
             mixer = build_part("mixer", "scored_attention", wide_norm=True, temperature=True, distance_table=(rows, m["bias_max"]),
                                chunk=m["mask"]["size"], sink="learned", cache_span=span, **common)

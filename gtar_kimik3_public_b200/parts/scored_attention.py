@@ -100,7 +100,7 @@ class ScoredAttention(Mixer):
         if self.wide_norm and (self.rot or self.unit_qk):
             raise ValueError("norms over whole rows come without rotation and unit lengths")
         self.distance_table = None if distance_table is None else (int(distance_table[0]), float(distance_table[1]))
-        self.dist_rows = None if self.distance_table is None else distance_rows(*self.distance_table)
+        self.dist_rows = None  # formed at load: the table's height is the tensor's
         self.chunk = None if not chunk else int(chunk)
         self.value_position, self.head_gate, self.own_kv = value_position, bool(head_gate), bool(own_kv)
         if value_position is not None and (int(value_position.dim) != self.dv or self.dv % 2):
@@ -159,9 +159,8 @@ class ScoredAttention(Mixer):
         if self.distance_table is not None:
             # one row a distance: the kernels read the term at min(distance, rows - 1) without forming the bucket
             rel = tensors[n["rel"]].float()
-            if rel.shape[0] != self.distance_table[0]:
-                self.distance_table = (int(rel.shape[0]), self.distance_table[1])
-                self.dist_rows = distance_rows(*self.distance_table)
+            self.distance_table = (int(rel.shape[0]), self.distance_table[1])
+            self.dist_rows = distance_rows(*self.distance_table)
             self.dist_bias = rel[torch.tensor(self.dist_rows, device=rel.device)].contiguous()
         if self.sink_kind == "learned":
             self.sink = tensors[n["sink"]].float().contiguous()

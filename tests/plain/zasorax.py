@@ -28,6 +28,12 @@ def mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return (a.to(LOWP).to(wide) @ b.to(LOWP).to(wide)).to(LOWP).to(wide)
 
 
+def kept(x: torch.Tensor) -> torch.Tensor:
+    """What a low-precision run stores between two products (queries, cached keys and values, read-outs): rounded to the
+    low precision; unchanged for the oracle."""
+    return x if LOWP is None else x.to(LOWP).to(x.dtype)
+
+
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     """x / sqrt(mean(x^2) + eps): eps inside the root."""
     return x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
@@ -74,9 +80,9 @@ def chunk_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float, kv: t
     head.  ``kv``: keys and values of another layer to read instead of own ones.  Returns (branch, (k, v))."""
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
-    q = (rms(mm(h, w[p + "q"].T), eps) * w[p + "q.norm"]).view(T, H, d)
+    q = kept(rms(mm(h, w[p + "q"].T), eps) * w[p + "q.norm"]).view(T, H, d)
     if kv is None:
-        k = (rms(mm(h, w[p + "k"].T), eps) * w[p + "k.norm"]).view(T, G, d)
+        k = kept(rms(mm(h, w[p + "k"].T), eps) * w[p + "k.norm"]).view(T, G, d)
         v = mm(h, w[p + "v"].T).view(T, G, dv)
     else:
         k, v = kv
@@ -84,13 +90,13 @@ def chunk_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float, kv: t
     rows, far, size = rel.shape[0], m["bias_max"], m["mask"]["size"]
     i = torch.arange(T)
     seen = (i[:, None] >= i[None, :]) & ((i[:, None] // size) == (i[None, :] // size))
-    row_of = torch.tensor([[distance_bucket(a - b, rows, far) if a >= b else 0 for b in range(T)] for a in range(T)])
+    row_of = torch.tensor([distance_bucket(n, rows, far) for n in range(T)])[(i[:, None] - i[None, :]).clamp_min(0)]
     outs = []
     for head in range(H):
         kh = head // (H // G)
         s = (q[:, head] @ k[:, kh].T) * m["scale"] * w[p + "temp"][head] + rel[:, head][row_of]
         outs.append(softmax_with_sink(s, seen, w[p + "sink"][head]) @ v[:, kh])
-    o = torch.stack(outs, 1).reshape(T, H * dv)
+    o = kept(torch.stack(outs, 1)).reshape(T, H * dv)
     return mm(o, w[p + "o"].T), (k, v)
 
 
@@ -101,10 +107,10 @@ def turned_value_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     T = h.shape[0]
     rot = m["rot"]
-    q = rms(turn(mm(h, w[p + "q"].T).view(T, H, d), rot["dims"], rot["base"]), eps)
+    q = kept(rms(turn(mm(h, w[p + "q"].T).view(T, H, d), rot["dims"], rot["base"]), eps))
     if kv is None:
-        k = rms(turn(mm(h, w[p + "k"].T).view(T, G, d), rot["dims"], rot["base"]), eps)
-        v = turn(mm(h, w[p + "v"].T).view(T, G, dv), dv, rot["base"])
+        k = kept(rms(turn(mm(h, w[p + "k"].T).view(T, G, d), rot["dims"], rot["base"]), eps))
+        v = kept(turn(mm(h, w[p + "v"].T).view(T, G, dv), dv, rot["base"]))
     else:
         k, v = kv
     i = torch.arange(T)
@@ -114,7 +120,7 @@ def turned_value_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float
         kh = head // (H // G)
         s = (q[:, head] @ k[:, kh].T) * m["scale"]
         outs.append(softmax_with_sink(s, seen, 0.0) @ v[:, kh])
-    o = turn(torch.stack(outs, 1), dv, rot["base"], backwards=True)
+    o = turn(kept(torch.stack(outs, 1)), dv, rot["base"], backwards=True)
     gate = torch.sigmoid(mm(h, w[p + "g"].T))  # [T, H]
     return mm((o * gate[:, :, None]).reshape(T, H * dv), w[p + "o"].T), (k, v)
 
@@ -129,10 +135,16 @@ def dense_ff(h: torch.Tensor, w: dict, p: str) -> torch.Tensor:
     return mm(xielu(mm(h, w[p + "up"].T), w[p + "act"]), w[p + "down"].T)
 
 
-def routed_ff(h: torch.Tensor, w: dict, p: str, mlp: dict) -> torch.Tensor:
-    """Router logits W_r h + b; the ``top`` largest are chosen and weighted by the softmax over the chosen logits alone."""
+def routed_ff(h: torch.Tensor, w: dict, p: str, mlp: dict, calls: list | None = None) -> torch.Tensor:
+    """Router logits W_r h + b; the ``top`` largest are chosen and weighted by the softmax over the chosen logits alone.
+    ``calls`` receives, per token, how far the last chosen logit lies above the first one not chosen, in units of the
+    logits' spread (infinite where every expert is chosen): a small number is a close call that rounding may decide."""
     n, top = mlp["router"]["experts"], mlp["router"]["top"]
-    z = h @ w[p + "router"].T + w[p + "router.b"]
+    seen = h if LOWP is None else h.to(LOWP).to(h.dtype)  # the router may read the rounding that the experts read
+    z = seen @ w[p + "router"].T + w[p + "router.b"]
+    if calls is not None:
+        ranked = z.sort(-1, descending=True).values
+        calls.append((ranked[:, top - 1] - ranked[:, top]) / z.std() if top < n else torch.full_like(z[:, 0], math.inf))
     best, ids = z.topk(top, dim=-1)
     share = torch.softmax(best, -1)
     out = torch.zeros_like(h)
@@ -150,8 +162,10 @@ def routed_ff(h: torch.Tensor, w: dict, p: str, mlp: dict) -> torch.Tensor:
 MIXERS = {"attention": chunk_attention, "attention_2": turned_value_attention}
 
 
-def forward(tokens: torch.Tensor, weights: dict, config: dict, dtype=torch.float64, keep_layers: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence.  ``keep_layers``: a list that receives the stream after every layer."""
+def forward(tokens: torch.Tensor, weights: dict, config: dict, dtype=torch.float64, keep_layers: list | None = None,
+            calls: list | None = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence.  ``keep_layers``: a list that receives the stream after every layer; ``calls``:
+    a list that receives every routed layer's margins (see ``routed_ff``)."""
     w = {name: (t.to(dtype) if t.is_floating_point() else t) for name, t in weights.items()}
     eps = config["norm"]["eps"]
     x = w["embed"][tokens] * (config.get("embedding") or {"scale": 1.0})["scale"]
@@ -163,7 +177,7 @@ def forward(tokens: torch.Tensor, weights: dict, config: dict, dtype=torch.float
         x = x + rms(branch, eps) * w[f"l{i}.norm1"]
         mlp = layer.get("mlp")
         if mlp is not None:
-            branch = dense_ff(x, w, f"l{i}.mlp.") if mlp["kind"] == "dense" else routed_ff(x, w, f"l{i}.mlp.", mlp)
+            branch = dense_ff(x, w, f"l{i}.mlp.") if mlp["kind"] == "dense" else routed_ff(x, w, f"l{i}.mlp.", mlp, calls)
             x = x + rms(branch, eps) * w[f"l{i}.norm2"]
         if keep_layers is not None:
             keep_layers.append(x)
