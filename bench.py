@@ -14,7 +14,7 @@ Weights are random (written as a model folder by the library's random-weights mo
 from there), token ids are seeded uniform-random: there is no network for checkpoints or data.
 The library runs on one GPU; with --gpus N > 1 a line says so and the exit code is 2.
 
-``--compare pofadra`` and ``--compare rezulorn`` do the same for the Pofadra and the Rezulorn decoders.  ``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
+``--compare pofadra`` and ``--compare rezulorn`` do the same for the Pofadra and the Rezulorn decoders; ``--compare zasorax`` puts the Zasorax decoder beside the Rezulorn decoder.  ``--compare dasusun`` runs another workload instead and prints its own JSON line: the Dasusun decoder beside the transformer
 at equal layer sizes (prefill and decode throughput of both, and the new design's kernels one by one against their rooflines).
 """
 
@@ -1250,6 +1250,233 @@ def run_compare_rezulorn(args) -> dict:
             "peaks": dict(peak, source=peak_source), "l2": "single kernels: a 192 MB buffer is written between the timed calls of the 2,048-token cases; the 8-token cases are 20 calls back to back from a CUDA graph",
             "results": results}
 
+# --compare zasorax: the Zasorax decoder (sublayers that read the stream itself and are normed on their way out; scored
+# attention in chunks with a distance table, head temperatures and learned sinks, some layers reading an earlier layer's
+# pages; causal attention with turned values, a fixed sink and a gate per head; dense xIELU and routed feed-forwards)
+# beside the Rezulorn decoder, whose attention kernels it shares, at equal width, and its kernels one by one beside the
+# like kernels of the models that were here.
+def _zasorax_config(width, layers, heads, kv_heads, dim, chunk, far, rows, t_heads, t_kv, rot, ff, experts, top, expert_ff, vocab):
+    chunked = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "bias_max": far, "mask": {"size": chunk},
+               "bias_rows": rows}
+    turned = {"heads": t_heads, "kv_heads": t_kv, "dim": dim, "vdim": dim, "scale": 0.3, "rot": {"base": 500000.0, "dims": rot}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+    stack = []
+    for i in range(layers):
+        place = i % 4
+        if place == 2:
+            stack.append({"type": "attention_2", "mixer": turned, "mlp": moe})
+        else:  # the fourth layer of every four reads the pages of the second
+            mixer = dict(chunked, kv_from=i - 2) if place == 3 else chunked
+            stack.append({"type": "attention", "mixer": mixer, "mlp": dense if place == 0 else moe})
+    return {"architecture": "Zasorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "layers": stack, "initializer_range": 0.02, "max_position_embeddings": 4096}
+
+
+ZASORAX_SIZES = {
+    # name: (Zasorax sizes, Rezulorn sizes); 8 layers each, vocabulary 32,768; a routed layer's chosen experts hold what
+    # a dense feed-forward of the other design holds
+    "width1024": (dict(width=1024, layers=8, heads=16, kv_heads=4, dim=64, chunk=1024, far=1024, rows=32, t_heads=16, t_kv=4, rot=32,
+                       ff=4096, experts=32, top=4, expert_ff=704, vocab=32768),
+                  REZULORN_SIZES["width1024"][0]),
+    "width2048": (dict(width=2048, layers=8, heads=16, kv_heads=4, dim=128, chunk=1024, far=1024, rows=32, t_heads=16, t_kv=4, rot=64,
+                       ff=8192, experts=32, top=4, expert_ff=1408, vocab=32768),
+                  REZULORN_SIZES["width2048"][0]),
+}
+
+
+def _zasorax_prefill_flops(d: dict, tokens: int) -> float:
+    w, dim = d["width"], d["dim"]
+    in_chunk = sum(t % d["chunk"] + 1 for t in range(tokens))
+    causal = tokens * (tokens + 1) // 2
+    dense = 4 * w * d["ff"]
+    routed = 6 * w * d["expert_ff"] * d["top"] + 2 * w * d["experts"]
+    own = 2 * w * (d["heads"] + 2 * d["kv_heads"]) * dim + 2 * d["heads"] * dim * w
+    reader = 2 * w * d["heads"] * dim + 2 * d["heads"] * dim * w
+    turned = 2 * w * ((d["t_heads"] + 2 * d["t_kv"]) * dim + d["t_heads"]) + 2 * d["t_heads"] * dim * w
+    total = 0.0
+    for i in range(d["layers"]):
+        place = i % 4
+        if place == 2:
+            total += (turned + routed) * tokens + 4 * d["t_heads"] * dim * causal
+        else:
+            total += ((reader if place == 3 else own) + (dense if place == 0 else routed)) * tokens + 4 * d["heads"] * dim * in_chunk
+    return total + 2 * w * d["vocab"]
+
+
+def _zasorax_kernel_table(d: dict, r: dict, peak: dict) -> dict:
+    """The new design's kernels alone and the like kernels of the models that were here (the Rezulorn decoder's scored
+    attention and cache writes, the transformer's residual add, the Pofadra decoder's whole-row norms, gate and router),
+    each with its share of its roofline."""
+    import torch
+
+    from gtar_kimik3_public_b200.ops import functional as F
+    from gtar_kimik3_public_b200.parts.scored_attention import distance_rows
+
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(48 << 20, dtype=torch.float32, device=dev)  # 192 MB: larger than the 126 MB L2
+    hbm, tflops = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+    out = {}
+
+    def record(name, ms, n_bytes, flops=0.0):
+        floor = max(n_bytes / hbm, flops / tflops) * 1e3
+        out[name] = {"us": round(ms * 1e3, 2), "roofline_us": round(floor * 1e3, 2), "frac": round(floor / ms, 4),
+                     "bound": "hbm" if n_bytes / hbm >= flops / tflops else "tensor"}
+
+    w, dim, chunk = d["width"], d["dim"], d["chunk"]
+    aq, ak, tq, tk = d["heads"], d["kv_heads"], d["t_heads"], d["t_kv"]
+    window, keep = r["window"], r["keep"]
+    bf = torch.bfloat16
+    for label, tokens, n_seqs in (("prefill_2048", 2048, 1), ("decode_b8_ctx2048", 8, 8)):
+        each = tokens // n_seqs
+        inner = 1 if n_seqs == 1 else 20
+        past = 0 if n_seqs == 1 else 2047
+        length = past + each
+        pages_each = -(-length // 64)
+        table = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).view(n_seqs, pages_each)
+        tok_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(each)
+        tok_pos = (torch.arange(each, dtype=torch.int32, device=dev) + past).repeat(n_seqs)
+        cu_q = torch.arange(n_seqs + 1, dtype=torch.int32, device=dev) * each
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        kv_len = torch.full((n_seqs,), length, dtype=torch.int32, device=dev)
+
+        def pages(n_heads, size):
+            return F.PagedKV(torch.randn(n_seqs * pages_each, n_heads, 64, size, device=dev).to(bf) * 0.1,
+                             torch.randn(n_seqs * pages_each, n_heads, 64, size, device=dev).to(bf) * 0.1, table, F.DecodeWork(dev))
+
+        # ---- the stream: a branch's norm, its add and the stream's copy, beside the add with the next norm
+        hs = torch.randn(tokens, w, device=dev)
+        branch = torch.randn(tokens, w, device=dev).to(bf)
+        wn = torch.ones(w, device=dev)
+        ms = _event_ms(lambda: F.branch_merge(hs, branch, wn, 1e-6, copy_dtype=bf), flush=flush, inner=inner)
+        record(f"zasorax branch norm, add and copy of the stream, {label}", ms, tokens * w * (4 + 2 + 4 + 2))
+        ms = _event_ms(lambda: F.add_rmsnorm(hs, branch, wn, 1e-6, bf), flush=flush, inner=inner)
+        record(f"transformer residual add with next norm, {label}", ms, tokens * w * (4 + 2 + 4 + 2))
+        ms = _event_ms(lambda: F.add_layernorm(hs, branch, wn, 1e-5, torch.float32, delta_scale=0.5), flush=flush, inner=inner)
+        record(f"rezulorn residual add with layer norm, {label}", ms, tokens * w * (4 + 2 + 4 + 4))
+        # ---- activations behind the first product of a dense feed-forward
+        wide_ff = torch.randn(tokens, d["ff"], device=dev).to(bf)
+        ms = _event_ms(lambda: F.xielu(wide_ff, 0.8, 1.2), flush=flush, inner=inner)
+        record(f"zasorax xIELU, {label}", ms, tokens * d["ff"] * 4)
+        ms = _event_ms(lambda: F.relu_squared(wide_ff), flush=flush, inner=inner)
+        record(f"rezulorn squared relu, {label}", ms, tokens * d["ff"] * 4)
+        # ---- routers
+        hb = torch.randn(tokens, w, device=dev).to(bf)
+        w_r, bias = torch.randn(d["experts"], w, device=dev) * 0.5, torch.randn(d["experts"], device=dev)
+        route_bytes = tokens * w * 2 + d["experts"] * w * 4 + tokens * d["top"] * 8
+        ms = _event_ms(lambda: F.route_groups(hb, w_r, bias, d["top"], 1, 1, 1.0, logits=True), flush=flush, inner=inner)
+        record(f"zasorax router (softmax over the chosen logits), {label}", ms, route_bytes)
+        ms = _event_ms(lambda: F.route_groups(hb, w_r, bias, d["top"], 4, 2, 2.5), flush=flush, inner=inner)
+        record(f"pofadra router (sigmoid scores, groups), {label}", ms, route_bytes)
+        # ---- between the projection and attention
+        kv = pages(ak, dim)
+        wide = torch.randn(tokens, (aq + 2 * ak) * dim, device=dev).to(bf)
+        wq, wk = torch.ones(aq * dim, device=dev), torch.ones(ak * dim, device=dev)
+        prep_bytes = tokens * 2 * ((aq + 2 * ak) * dim + aq * dim + 2 * ak * dim)
+        ms = _event_ms(lambda: F.wide_norm_rope_write(wide, aq, ak, dim, wq, wk, 1e-6, None, None, 0, tok_pos, tok_seq, slots, kv, length - 1,
+                                                      v_at=(aq + ak) * dim), flush=flush, inner=inner)
+        record(f"zasorax whole-row norms and cache write (own values), {label}", ms, prep_bytes)
+        ms = _event_ms(lambda: F.wide_norm_rope_write(wide, aq, ak, dim, wq, wk, 1e-6, None, None, 0, tok_pos, tok_seq, slots, kv, length - 1),
+                       flush=flush, inner=inner)
+        record(f"pofadra whole-row norms and cache write (values are the keys), {label}", ms, tokens * 2 * ((aq + ak) * dim + aq * dim + 2 * ak * dim))
+        ms = _event_ms(lambda: F.heads_prepare(wide, 0, aq * dim, (aq + ak) * dim, aq, ak, dim, dim, tok_pos, tok_seq, slots, kv=kv,
+                                               max_position=length - 1), flush=flush, inner=inner)
+        record(f"rezulorn cache write (no rotation), {label}", ms, prep_bytes)
+        angle = torch.arange(length, dtype=torch.float32, device=dev)[:, None] * torch.rand(d["rot"] // 2, device=dev)[None, :]
+        cos, sin = angle.cos().contiguous(), angle.sin().contiguous()
+        v_angle = torch.arange(length, dtype=torch.float32, device=dev)[:, None] * torch.rand(dim // 2, device=dev)[None, :]
+        v_cos, v_sin = v_angle.cos().contiguous(), v_angle.sin().contiguous()
+        kvt = pages(tk, dim)
+        widet = torch.randn(tokens, (tq + 2 * tk) * dim + 8 * -(-tq // 8), device=dev).to(bf)
+        prep_t = tokens * 2 * ((tq + 2 * tk) * dim + tq * dim + 2 * tk * dim)
+        ms = _event_ms(lambda: F.heads_prepare(widet, 0, tq * dim, (tq + tk) * dim, tq, tk, dim, dim, tok_pos, tok_seq, slots, rot=d["rot"],
+                                               cos=cos, sin=sin, unit_eps=1e-6, kv=kvt, max_position=length - 1, v_cos=v_cos, v_sin=v_sin),
+                       flush=flush, inner=inner)
+        record(f"zasorax rotation, unit q and k, turned values, cache write, {label}", ms, prep_t)
+        ms = _event_ms(lambda: F.heads_prepare(widet, 0, tq * dim, (tq + tk) * dim, tq, tk, dim, dim, tok_pos, tok_seq, slots, rot=d["rot"],
+                                               cos=cos, sin=sin, unit_eps=1e-6, kv=kvt, max_position=length - 1), flush=flush, inner=inner)
+        record(f"rezulorn rotation, unit q and k, cache write, {label}", ms, prep_t)
+        # ---- attention
+        qa = torch.randn(tokens, aq, dim, device=dev).to(bf)
+        rel = torch.randn(d["rows"], aq, device=dev)
+        dist = rel[torch.tensor(distance_rows(d["rows"], d["far"]), device=dev)].contiguous()
+        temp, sink = torch.full((aq,), 0.9, device=dev), torch.full((aq,), 0.5, device=dev)
+        seen = sum(p % chunk + 1 for p in range(past, length)) * n_seqs
+        longest = min(length, chunk + each)
+        parts = F.scored_attention_parts(n_seqs, aq, ak, each, -(-chunk // 64) + 2, F.sm_count(dev))
+        ms = _event_ms(lambda: F.attention_scored(qa, kv, cu_q, kv_len, slots, each, dim ** -0.5, n_parts=parts, chunk=chunk, temp=temp,
+                                                  dist_bias=dist, sink=sink), flush=flush, inner=inner)
+        attn_bytes = 2 * (2 * tokens * aq * dim + 2 * n_seqs * longest * ak * dim)
+        record(f"zasorax attention: chunks of {chunk}, distance table, head temperature, learned sink, {label}", ms, attn_bytes,
+               4 * aq * dim * seen)
+        ms = _event_ms(lambda: F.attention_scored_exact(qa, kv, tok_pos, tok_seq, slots, dim ** -0.5, chunk=chunk, temp=temp, dist_bias=dist,
+                                                        sink=sink), flush=flush, inner=inner, repeats=3)
+        record(f"zasorax attention, the same on the exact kernel (what 32-bit runs use), {label}", ms, attn_bytes, 4 * aq * dim * seen)
+        r1, r2 = torch.full((aq,), 0.3, device=dev), torch.full((aq,), 0.5, device=dev)
+        seen_r = sum(min(p + 1, window) + min(keep, max(0, p + 1 - window)) for p in range(past, length)) * n_seqs
+        parts = F.scored_attention_parts(n_seqs, aq, ak, each, -(-(window + keep) // 64) + 2, F.sm_count(dev))
+        ms = _event_ms(lambda: F.attention_scored(qa, kv, cu_q, kv_len, slots, each, dim ** -0.5, window, keep, r1, r2, None, "softmax", parts),
+                       flush=flush, inner=inner)
+        record(f"rezulorn attention: distance term, window {window} keeping {keep}, softmax, {label}", ms,
+               2 * (2 * tokens * aq * dim + 2 * n_seqs * min(length, window + keep + each) * ak * dim), 4 * aq * dim * seen_r)
+        qt = torch.randn(tokens, tq, dim, device=dev).to(bf)
+        zero = torch.zeros(tq, device=dev)
+        causal = sum(p + 1 for p in range(past, length)) * n_seqs
+        parts = F.scored_attention_parts(n_seqs, tq, tk, each, pages_each, F.sm_count(dev))
+        causal_bytes = 2 * (2 * tokens * tq * dim + 2 * n_seqs * length * tk * dim)
+        ms = _event_ms(lambda: F.attention_scored(qt, kvt, cu_q, kv_len, slots, each, 0.3, n_parts=parts, sink=zero), flush=flush, inner=inner)
+        record(f"zasorax attention: causal, one added to the denominator, {label}", ms, causal_bytes, 4 * tq * dim * causal)
+        pb = torch.full((tq,), -4.0, device=dev)
+        ms = _event_ms(lambda: F.attention_scored(qt, kvt, cu_q, kv_len, slots, each, 0.3, 0, 0, None, None, pb, "sigmoid", parts),
+                       flush=flush, inner=inner)
+        record(f"rezulorn attention: causal, sigmoid weights, {label}", ms, causal_bytes, 4 * tq * dim * causal)
+        # ---- behind attention
+        gate_at = (tq + 2 * tk) * dim
+        ms = _event_ms(lambda: F.turn_back_gate(qt, v_cos, v_sin, tok_pos, length - 1, widet, gate_at), flush=flush, inner=inner)
+        record(f"zasorax read-outs turned back, gate per head, {label}", ms, tokens * tq * dim * 4)
+        flat = qt.view(tokens, tq * dim)
+        gates = torch.randn(tokens, tq * dim, device=dev).to(bf)
+        ms = _event_ms(lambda: F.sigmoid_gate(flat, gates, 0), flush=flush, inner=inner)
+        record(f"pofadra gate per entry, {label}", ms, tokens * tq * dim * 6)
+    return out
+
+
+def run_compare_zasorax(args) -> dict:
+    import gc
+
+    import torch
+
+    from gtar_kimik3_public_b200.ops.library import require_device
+
+    require_device(torch.device("cuda:0"))
+    peak, peak_source = peaks()
+    results = {}
+    for name, (d, r) in ZASORAX_SIZES.items():
+        entry = {}
+        for arch, raw, flops in (("zasorax", _zasorax_config(**d), _zasorax_prefill_flops(d, PREFILL_TOKENS)),
+                                 ("rezulorn", _rezulorn_config(**r), _rezulorn_prefill_flops(r, PREFILL_TOKENS))):
+            model = _device_model(raw)
+            ms = _time_prefill_ms(model, PREFILL_TOKENS)
+            decode = time_decode(model, args.batch, min(args.steps, 64), args.warmup)
+            entry[arch] = {
+                "weight_bytes_per_step": model.weight_bytes_per_step(),
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / (ms / 1e3), 1), "prefill_ms": round(ms, 3),
+                "prefill_frac_of_bf16_peak": round(flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                "decode_frac_of_hbm_peak": round(decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4),
+                "decode_launches_per_step": decode["launches"] // max(1, min(args.steps, 64)),
+            }
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        entry["kernels"] = _zasorax_kernel_table(d, r, peak)
+        results[name] = {"sizes": {"zasorax": d, "rezulorn": r}, **entry}
+    return {"compare": "zasorax beside rezulorn at equal width", "batch": args.batch, "prompt_tokens": PROMPT_LEN,
+            "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16", "data": "synthetic: random token ids, random weights drawn on the device",
+            "peaks": dict(peak, source=peak_source), "l2": "single kernels: a 192 MB buffer is written between the timed calls of the 2,048-token cases; the 8-token cases are 20 calls back to back from a CUDA graph",
+            "results": results}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -1259,13 +1486,13 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--no-large", action="store_true", help="leave out the points at the 4B and 8B layer sizes")
-    parser.add_argument("--compare", default=None, choices=["dasusun", "pofadra", "rezulorn"],
+    parser.add_argument("--compare", default=None, choices=["dasusun", "pofadra", "rezulorn", "zasorax"],
                         help="instead of the default workload: this architecture beside the transformer at equal layer sizes")
     args = parser.parse_args()
     if args.compare:
         if args.warmup < 3:
             args.warmup = 3
-        runner = {"pofadra": run_compare_pofadra, "rezulorn": run_compare_rezulorn, "dasusun": run_compare}[args.compare]
+        runner = {"pofadra": run_compare_pofadra, "rezulorn": run_compare_rezulorn, "zasorax": run_compare_zasorax, "dasusun": run_compare}[args.compare]
         print(json.dumps(runner(args)))
         return 0
     if args.impl == "reference":

@@ -44,6 +44,7 @@ struct GemvParams {
     int n, k, tokens;
     long long ldw, ldx, ldo;
     int out_f32, swiglu;
+    float act_a, act_b;       // the two constants of output stage 4
     // Optional: the activations are the RMSNorm of the rows of a 32-bit stream, formed here (`norm_h` set, `x` unused):
     //   x[t, k] = bfloat16((h[t, k] * rsqrt(mean_k h[t, k]^2 + eps)) * norm_w[k])       (src/layers/rmsnorm.py:11-16)
     // every block holds whole rows of its tokens (its threads' pieces of a row are the row), so it forms the row's
@@ -176,6 +177,9 @@ __global__ void __launch_bounds__(THREADS, NORM || XR > X_REGS ? 2 : ROW_SETS ==
                 b = fmaxf(b, 0.f);
                 a *= a;
                 b *= b;
+            } else if (p.swiglu == 4) {  // quadratic above zero, exponential below: act_a z^2 + z/2, act_b (exp(z) - 1 - z) + z/2
+                a = a > 0.f ? fmaf(p.act_a * a, a, 0.5f * a) : fmaf(p.act_b, expm1f(a) - a, 0.5f * a);
+                b = b > 0.f ? fmaf(p.act_a * b, b, 0.5f * b) : fmaf(p.act_b, expm1f(b) - b, 0.5f * b);
             }
             if (p.resid) {
                 float* o = p.resid + (size_t)token * p.ldr + col;
@@ -508,16 +512,17 @@ int launch_gemv(GemvParams& p, cudaStream_t stream) {
 
 // OUT[t, :] = x[t, :] @ w^T for 1 to 16 tokens (17 to 32 where 257 <= k <= 1024) and up to 64 weight rows per SM; `w` [n, k] and `x` [tokens, k]
 // bfloat16 with rows in steps of 8 elements (16 bytes); OUT bfloat16 or float32, [tokens, n], or with `swiglu` = 1
-// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows; `swiglu` = 2 stores gelu_tanh of every result, 3 the square of its relu.
+// [tokens, n / 2] bfloat16 = silu(even rows) * odd rows; `swiglu` = 2 stores gelu_tanh of every result, 3 the square of its relu,
+// 4 the activation that is act_a z^2 + z/2 above zero and act_b (exp(z) - 1 - z) + z/2 below.
 GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const void* x, int tokens, long long ldx, void* out,
-                           int out_dtype, int swiglu, void* stream) {
+                           int out_dtype, int swiglu, float act_a, float act_b, void* stream) {
     GK_REQUIRE(n > 0 && k > 0 && tokens > 0 && tokens <= 32, "gemv: takes 1 to 32 tokens and positive sizes; got %d tokens, n=%d k=%d",
                tokens, n, k);
     GK_REQUIRE(k % 8 == 0 && ldw % 8 == 0 && ldx % 8 == 0, "gemv: k and the row strides must be multiples of 8 elements; got k=%d ldw=%lld ldx=%lld",
                k, ldw, ldx);
     GK_REQUIRE(((uintptr_t)w & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 3) == 0, "gemv: operands must be 16-byte aligned");
     GK_REQUIRE(GK_VALID_DTYPE(out_dtype), "gemv: bad output dtype");
-    GK_REQUIRE(swiglu >= 0 && swiglu <= 3, "gemv: output stage %d is none of store, SwiGLU, GELU, squared relu", swiglu);
+    GK_REQUIRE(swiglu >= 0 && swiglu <= 4, "gemv: output stage %d is none of store, SwiGLU, GELU, squared relu, xIELU", swiglu);
     GK_REQUIRE(swiglu != 1 || (n % 2 == 0 && out_dtype == GK_BF16), "gemv: the SwiGLU output stage needs an even number of rows and writes bfloat16");
     GemvParams p = {};
     p.w = (const __nv_bfloat16*)w;
@@ -531,6 +536,8 @@ GK_EXPORT int gk_gemv_bf16(const void* w, int n, int k, long long ldw, const voi
     p.ldo = swiglu == 1 ? n / 2 : n;
     p.out_f32 = out_dtype == GK_F32;
     p.swiglu = swiglu;
+    p.act_a = act_a;
+    p.act_b = act_b;
     return launch_gemv(p, (cudaStream_t)stream);
 }
 

@@ -430,12 +430,13 @@ def gemv_suits(m: int, n: int, k: int, device: torch.device) -> bool:
 
 
 def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, swiglu: bool = False,
-         out: torch.Tensor | None = None, gelu: bool = False, relu_squared: bool = False) -> torch.Tensor:
+         out: torch.Tensor | None = None, gelu: bool = False, relu_squared: bool = False,
+         xielu: tuple[float, float] | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T`` for up to 16 tokens (32 where ``gemv_suits`` says so): weights go from memory straight into registers and
     through ``mma.sync`` with 32-bit accumulation; made for the latency of a decode step, where a projection
     is a few megabytes of weights and next to no arithmetic.  ``swiglu`` as in ``gemm_tc``; ``gelu`` stores the tanh form
     of GELU of every result (the 32-bit sums go through it before they are rounded), ``relu_squared`` the square of its
-    relu."""
+    relu, ``xielu = (up, down)`` the activation ``up z^2 + z/2`` above zero and ``down (exp(z) - 1 - z) + z/2`` below."""
     require_device(x.device)
     _check(x, "x", torch.bfloat16, 2)
     _check(weight, "weight", torch.bfloat16, 2)
@@ -447,8 +448,8 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.b
         raise KernelError(f"gemv takes up to {GEMV_MAX_TOKENS_SHORT_K} tokens, got {m}")
     if swiglu and n % 2:
         raise KernelError("the SwiGLU epilogue needs an even number of weight rows")
-    if swiglu + gelu + relu_squared > 1:
-        raise KernelError("one output stage at a time: SwiGLU, GELU or squared relu")
+    if swiglu + gelu + relu_squared + (xielu is not None) > 1:
+        raise KernelError("one output stage at a time: SwiGLU, GELU, squared relu or xIELU")
     n_out = n // 2 if swiglu else n
     if out is None:
         out = torch.empty((m, n_out), dtype=out_dtype, device=x.device)
@@ -456,7 +457,8 @@ def gemv(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype = torch.b
     if tuple(out.shape) != (m, n_out):
         raise KernelError(f"out has shape {tuple(out.shape)}, expected {(m, n_out)}")
     call("gk_gemv_bf16", ptr(weight), n, k, k, ptr(x), m, k, ptr(out), dtype_code(out_dtype),
-         3 if relu_squared else 2 if gelu else int(swiglu), stream_ptr())
+         4 if xielu is not None else 3 if relu_squared else 2 if gelu else int(swiglu), float(xielu[0]) if xielu else 0.0,
+         float(xielu[1]) if xielu else 0.0, stream_ptr())
     return out
 
 

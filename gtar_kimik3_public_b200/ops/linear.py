@@ -29,16 +29,25 @@ def _tc_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           swiglu: bool = False, gelu: bool = False, relu_squared: bool = False) -> torch.Tensor:
+           swiglu: bool = False, gelu: bool = False, relu_squared: bool = False,
+           xielu: tuple[float, float] | None = None) -> torch.Tensor:
     """``x [M, K] @ weight[N, K].T -> [M, N]`` in ``out_dtype`` (default: ``x.dtype``).
 
     ``swiglu``: ``weight`` holds gate and up rows alternately and the result is ``silu(gate) * up``
     of width ``N / 2``.  ``gelu``: the tanh form of GELU of the result; where the few-token product runs it is that
     kernel's output stage (applied to the 32-bit sums), elsewhere a kernel of its own behind the product.
-    ``relu_squared``: the square of the result's relu, in the same two ways.
+    ``relu_squared``: the square of the result's relu, in the same two ways.  ``xielu = (up, down)``: the activation
+    ``up z^2 + z/2`` above zero and ``down (exp(z) - 1 - z) + z/2`` below, in the same two ways.
     """
     require_device(x.device)
     out_dtype = out_dtype or x.dtype
+    if xielu is not None:
+        if swiglu or gelu or relu_squared:
+            raise KernelError("one activation at a time: SwiGLU, GELU, squared relu or xIELU")
+        if (weight.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and _tc_ok(x, weight)
+                and F.gemv_suits(x.shape[0], weight.shape[0], x.shape[1], x.device)):
+            return F.gemv(x, weight, out_dtype, xielu=xielu)
+        return F.xielu(linear(x, weight, out_dtype), *xielu)
     if relu_squared:
         if swiglu or gelu:
             raise KernelError("one activation at a time: SwiGLU, GELU or squared relu")

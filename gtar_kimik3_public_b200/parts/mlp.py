@@ -122,8 +122,8 @@ class XieluFeedForward(FeedForward):
 
         z > 0:   softplus(p) z^2 + z / 2          z <= 0:   (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
 
-    No gate, no biases.  The two constants are formed once at load, in 32-bit; the activation is a kernel of its own
-    behind the product and works in 32-bit on what the product hands on."""
+    No gate, no biases.  The two constants are formed once at load, in 32-bit; the activation is the output stage of the
+    few-token product (applied to its 32-bit sums) and a kernel of its own behind the many-token product."""
 
     graph_safe = True
 
@@ -148,7 +148,7 @@ class XieluFeedForward(FeedForward):
         return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
 
     def forward(self, x, ctx: StepContext) -> torch.Tensor:
-        return linear(F.xielu(linear(x, self.w_up), self.up_const, self.down_const), self.w_down)
+        return linear(linear(x, self.w_up, xielu=(self.up_const, self.down_const)), self.w_down)
 
 
 register_part("feed_forward", "xielu", XieluFeedForward)
