@@ -1466,6 +1466,15 @@ def run_compare_zasorax(args) -> dict:
                 "decode_frac_of_hbm_peak": round(decode["bytes_per_step"] / (decode["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4),
                 "decode_launches_per_step": decode["launches"] // max(1, min(args.steps, 64)),
             }
+            if arch == "zasorax":
+                # a step's weight bytes count the experts ONE token reads; a batch reads every distinct expert its tokens
+                # choose: with uniform choices E (1 - (1 - top / E)^batch) of them in every routed layer
+                distinct = d["experts"] * (1.0 - (1.0 - d["top"] / d["experts"]) ** args.batch)
+                routed_layers = sum(1 for i in range(d["layers"]) if i % 4 != 0)
+                more = routed_layers * (distinct - d["top"]) * 3 * d["expert_ff"] * d["width"] * 2
+                entry[arch]["decode_expected_distinct_experts"] = round(distinct, 1)
+                entry[arch]["decode_frac_of_hbm_peak_with_distinct_experts"] = round(
+                    (decode["bytes_per_step"] + more) / (decode["ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4)
             del model
             gc.collect()
             torch.cuda.empty_cache()

@@ -85,10 +85,11 @@ class ZasoraxConfig(ModelConfig):
             if kind not in MIXERS:
                 raise ConfigError(f"ZasoraxConfig: {where}.type {kind!r} is not a mixer of this design (known: {list(MIXERS)})")
             if kind == "attention":
-                m = _need(where + ".mixer", layer["mixer"], ("heads", "kv_heads", "dim", "vdim", "scale", "bias_max", "mask"),
-                          ("kv_from", "bias_rows"))
+                m = _need(where + ".mixer", layer["mixer"], ("heads", "kv_heads", "dim", "vdim", "scale", "bias_max"),
+                          ("kv_from", "bias_rows", "mask"))
                 _positive(f"{where}.mixer.bias_max", m["bias_max"])
-                _positive_int(f"{where}.mixer.mask.size", _need(where + ".mixer.mask", m["mask"], ("size",))["size"])
+                if m.get("mask") is not None:  # absent: every earlier key is seen
+                    _positive_int(f"{where}.mixer.mask.size", _need(where + ".mixer.mask", m["mask"], ("size",))["size"])
                 if m.get("bias_rows") is not None and _positive_int(f"{where}.mixer.bias_rows", m["bias_rows"]) < 2:
                     raise ConfigError(f"ZasoraxConfig: {where}.mixer.bias_rows must be at least 2")
             else:

@@ -44,14 +44,18 @@ __device__ __forceinline__ float lg2_fast(float x) {
     return y;
 }
 
-template <int D, bool SIGMOID>
-__global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
+// MORE: which of the further rules are compiled in: 0 none, 1 the sink alone, 2 the chunk, the head temperature, the
+// distance table and the sink.  Without them the kernel is the windowed one alone and keeps its registers (a third block
+// a multiprocessor at heads of 64); the sink alone costs none.
+template <int D, bool SIGMOID, int MORE>
+__global__ void __launch_bounds__(SC_WARPS * 32, (MORE == 2 && D == 64) ? 3 : 0) attention_scored_mma_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages, const __nv_bfloat16* __restrict__ v_pages,
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ cu_q,
     const int* __restrict__ kv_len, const int* __restrict__ slots, const int* __restrict__ block_table, int n_tokens, int n_q,
     int n_kv, int max_pages, float sl2, int window, int keep_first, const float* __restrict__ r1, const float* __restrict__ r2,
     const float* __restrict__ head_bias, int n_split, int chunk, const float* __restrict__ temp,
     const float* __restrict__ dist_bias, int n_dist, const float* __restrict__ sink) {
+    constexpr bool RULES = MORE == 2;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     ScoredSmem<D>& sm = *reinterpret_cast<ScoredSmem<D>*>(smem_raw);
     pdl_launch_dependents();
@@ -80,8 +84,8 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
         tok[h] = row_ok[h] ? r / group : 0;
         pos[h] = past + tok[h];
         head[h] = hk * group + (row_ok[h] ? r % group : 0);
-        first[h] = chunk > 0 ? (pos[h] / chunk) * chunk : 0;
-        sl2h[h] = temp != nullptr ? sl2 * temp[head[h]] : sl2;
+        first[h] = RULES && chunk > 0 ? (pos[h] / chunk) * chunk : 0;
+        sl2h[h] = RULES && temp != nullptr ? sl2 * temp[head[h]] : sl2;
         b1[h] = r1 != nullptr ? r1[head[h]] : 0.f;  // the distance term in the base-2 domain: r1 log2(1 + r2 gap)
         b2[h] = r1 != nullptr ? r2[head[h]] : 0.f;
         add[h] = head_bias != nullptr ? head_bias[head[h]] * LOG2E : 0.f;
@@ -106,7 +110,7 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     const int max_pos = past + last_row / group;
     const int min_pos = past + row0 / group;
     int lo_block = (window > 0 && min_pos - window + 1 > 0) ? min_pos - window + 1 : 0;
-    if (chunk > 0) {
+    if (RULES && chunk > 0) {
         const int chunk_first = (min_pos / chunk) * chunk;  // no row of the block sees a key before its first row's chunk
         if (chunk_first > 0) keep_first = 0;                // the kept first keys lie in an earlier chunk
         lo_block = max(lo_block, chunk_first);
@@ -120,7 +124,7 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     const int w_max_pos = w_last_row >= wrow0 ? past + w_last_row / group : -1;
     const int w_min_pos = past + wrow0 / group;
     int w_lo = (window > 0 && w_min_pos - window + 1 > 0) ? w_min_pos - window + 1 : 0;
-    if (chunk > 0) w_lo = max(w_lo, (w_min_pos / chunk) * chunk);
+    if (RULES && chunk > 0) w_lo = max(w_lo, (w_min_pos / chunk) * chunk);
 
     auto page_index = [&](int it) { return it < kept_pages ? it : p_begin + it - kept_pages; };
     auto issue = [&](int it) {
@@ -137,7 +141,7 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
     };
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    if (!SIGMOID && sink != nullptr && split == 0) {
+    if (MORE >= 1 && !SIGMOID && sink != nullptr && split == 0) {
         // the sink opens the running softmax of the first part: a term exp(sink) in the denominator that carries no value
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -173,10 +177,10 @@ __global__ void __launch_bounds__(SC_WARPS * 32) attention_scored_mma_kernel(
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int gap = pos[h] - key;
-                        const bool hidden = gap < 0 || (window > 0 && gap >= window && key >= keep_first) || key < first[h];
-                        float t = s[n][2 * h + c] * sl2h[h];
+                        const bool hidden = gap < 0 || (window > 0 && gap >= window && key >= keep_first) || (RULES && key < first[h]);
+                        float t = s[n][2 * h + c] * (RULES ? sl2h[h] : sl2);
                         if (biased) t -= b1[h] * lg2_fast(fmaf(b2[h], (float)max(gap, 0), 1.f));
-                        if (dist_bias != nullptr)
+                        if (RULES && dist_bias != nullptr)
                             t = fmaf(__ldg(dist_bias + (size_t)min(max(gap, 0), n_dist - 1) * n_q + head[h]), LOG2E, t);
                         if (SIGMOID)
                             s[n][2 * h + c] = hidden ? 0.f : __fdividef(1.f, 1.f + exp2_fast(-(t + add[h])));
@@ -255,7 +259,7 @@ __global__ void __launch_bounds__(128) attention_scored_join_kernel(const float*
     for (int c = 0; c < D / 32; ++c) out[(size_t)item * D + lane + 32 * c] = __float2bfloat16(acc[c] * inv);
 }
 
-template <int D, bool SIGMOID>
+template <int D, bool SIGMOID, int MORE>
 int launch_scored(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o, float* part_ml, const int* cu_q,
                   const int* kv_len, const int* slots, const int* block_table, int n_seqs, int max_q_len, int n_tokens, int n_q,
                   int n_kv, int max_pages, float scale, int window, int keep_first, const float* r1, const float* r2,
@@ -264,14 +268,14 @@ int launch_scored(const void* q, const void* k_pages, const void* v_pages, void*
     const size_t smem = sizeof(ScoredSmem<D>);
     static bool configured = false;
     if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attention_scored_mma_kernel<D, SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(attention_scored_mma_kernel<D, SIGMOID, MORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return gk_fail(GK_CUDA_ERROR, "attention_scored_mma: %s", cudaGetErrorString(err));
         configured = true;
     }
     const int group = n_q / n_kv;
     const long long blocks = (((long long)max_q_len * group + SC_ROWS - 1) / SC_ROWS) * n_split;
     GK_REQUIRE(blocks <= 2147483647LL, "attention_scored_mma: too many rows");
-    gk_launch(attention_scored_mma_kernel<D, SIGMOID>, dim3((unsigned)blocks, n_kv, n_seqs), dim3(SC_WARPS * 32), smem, stream,
+    gk_launch(attention_scored_mma_kernel<D, SIGMOID, MORE>, dim3((unsigned)blocks, n_kv, n_seqs), dim3(SC_WARPS * 32), smem, stream,
               (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, (__nv_bfloat16*)out, part_o, part_ml,
               cu_q, kv_len, slots, block_table, n_tokens, n_q, n_kv, max_pages, scale * LOG2E, window, keep_first, r1, r2, head_bias,
               n_split, chunk, temp, dist_bias, n_dist, sink);
@@ -310,10 +314,21 @@ GK_EXPORT int gk_attention_scored_bf16(const void* q, const void* k_pages, const
     GK_REQUIRE(sink == nullptr || weights == 0, "attention_scored_mma: a sink belongs to the softmax");
     if (n_seqs == 0 || max_q_len == 0 || n_tokens == 0) return GK_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    const int more = (chunk > 0 || temp != nullptr || dist_bias != nullptr) ? 2 : sink != nullptr ? 1 : 0;
 #define GK_SCORED(D, SIG)                                                                                                             \
-    return launch_scored<D, SIG>(q, k_pages, v_pages, out, part_o, part_ml, cu_q, kv_len, slots, block_table, n_seqs, max_q_len,      \
-                                 n_tokens, n_q, n_kv, max_pages, scale, window, keep_first, r1, r2, head_bias, n_split, chunk, temp,  \
-                                 dist_bias, n_dist, sink, s)
+    do {                                                                                                                              \
+        if (more == 2)                                                                                                                \
+            return launch_scored<D, SIG, 2>(q, k_pages, v_pages, out, part_o, part_ml, cu_q, kv_len, slots, block_table, n_seqs,      \
+                                            max_q_len, n_tokens, n_q, n_kv, max_pages, scale, window, keep_first, r1, r2,             \
+                                            head_bias, n_split, chunk, temp, dist_bias, n_dist, sink, s);                             \
+        if (more == 1)                                                                                                                \
+            return launch_scored<D, SIG, 1>(q, k_pages, v_pages, out, part_o, part_ml, cu_q, kv_len, slots, block_table, n_seqs,      \
+                                            max_q_len, n_tokens, n_q, n_kv, max_pages, scale, window, keep_first, r1, r2,             \
+                                            head_bias, n_split, chunk, temp, dist_bias, n_dist, sink, s);                             \
+        return launch_scored<D, SIG, 0>(q, k_pages, v_pages, out, part_o, part_ml, cu_q, kv_len, slots, block_table, n_seqs,      \
+                                            max_q_len, n_tokens, n_q, n_kv, max_pages, scale, window, keep_first, r1, r2, head_bias,  \
+                                            n_split, chunk, temp, dist_bias, n_dist, sink, s);                                        \
+    } while (0)
     if (head_dim == 64) {
         if (weights == 1) GK_SCORED(64, true);
         GK_SCORED(64, false);

@@ -55,9 +55,10 @@ def build_zasorax_plan(config: ZasoraxConfig) -> ModelPlan:
         if spec["type"] == "attention":
             # what the random-weights mode writes (half the rows must lie below bias_max); a model file's tensor has the last word
             rows = m.get("bias_rows") or max(2, min(DEFAULT_BIAS_ROWS, 2 * (math.ceil(m["bias_max"]) - 1)))
-            span = max(r["mask"]["size"] for r in readers[i if source is None else source])
+            chunks = [(r.get("mask") or {}).get("size") for r in readers[i if source is None else source]]
+            span = None if None in chunks else max(chunks)  # a reader without chunks needs every page kept
             mixer = build_part("mixer", "scored_attention", wide_norm=True, temperature=True, distance_table=(rows, m["bias_max"]),
-                               chunk=m["mask"]["size"], sink="learned", cache_span=span, **common)
+                               chunk=(m.get("mask") or {}).get("size"), sink="learned", cache_span=span, **common)
         else:
             rot = m["rot"]
             mixer = build_part("mixer", "scored_attention", position=rotation(rot["dims"], rot["base"]), unit_qk=True, sink="zero",

@@ -34,7 +34,7 @@ Further rules, each switched on by the builder:
   ``[heads, hidden]``, packed behind the other input projections), before the output projection;
 * ``own_kv`` False: the layer has no key and value tensors and reads the pages of an earlier layer (the model's run
   list names it), with its own queries and rules; ``cache_span`` is then, for the layer that owns the pages, how far
-  back any of their readers look.
+  back any of their readers look (None: every page is kept; by default the layer's own window or chunk).
 
 Scores, weights and the sums over keys are 32-bit.  A step's kernels: the packed projection q | k | v | g; one kernel for
 norms, rotation, unit lengths and the cache write; attention over the pages (on the tensor cores in bfloat16 with keys and
@@ -78,7 +78,7 @@ class ScoredAttention(Mixer):
                  names: dict[str, str] | None = None, wide_norm: bool = False, temperature: bool = False,
                  distance_table: tuple[int, float] | None = None, chunk: int | None = None, sink: str | None = None,
                  value_position: PositionEncoding | None = None, head_gate: bool = False, own_kv: bool = True,
-                 cache_span: int | None = None):
+                 cache_span: int | None | str = "own"):
         if n_q_heads % n_kv_heads:
             raise ValueError("query heads must be a multiple of key heads")
         if weights not in ("softmax", "sigmoid"):
@@ -107,7 +107,10 @@ class ScoredAttention(Mixer):
             raise ValueError(f"values of {self.dv} entries turn over all of them: the tables must have {self.dv} / 2 angles")
         # how far back the pages must reach: the layer's own window or chunk, or what the builder says their readers need
         spans = [s for s in (self.window, self.chunk) if s]
-        self.cache_span = int(cache_span) if cache_span else (min(spans) if spans else None)
+        if cache_span == "own":
+            self.cache_span = min(spans) if spans else None
+        else:  # the builder's word: a number of positions, or None for all
+            self.cache_span = int(cache_span) if cache_span else None
         self.names = {**_NAMES, **(names or {})}
         self.w_in = self.w_o = self.r1 = self.r2 = self.pb = None
         self.q_norm = self.k_norm = self.temp = self.dist_bias = self.sink = None

@@ -110,7 +110,7 @@ def _changed(path, value):
 
 @pytest.mark.parametrize("change,message", [
     ((("layers", 0, "type"), "lightning"), "not a mixer"),
-    ((("layers", 0, "mixer", "mask"), KeyError), "missing keys ['mask']"),
+    ((("layers", 0, "mixer", "mask"), {}), "missing keys ['size']"),
     ((("layers", 0, "mixer", "bias_max"), 0), "bias_max"),
     ((("layers", 1, "mixer", "rot"), KeyError), "missing keys ['rot']"),
     ((("layers", 1, "mixer", "rot", "dims"), 26), "rot.dims"),
@@ -132,6 +132,14 @@ def test_configuration_errors_name_the_key(change, message):
     with pytest.raises(ConfigError) as caught:
         config_from_dict(_changed(*change))
     assert message in str(caught.value)
+
+
+def test_a_layer_without_chunks_sees_everything_and_keeps_every_page():
+    raw = copy.deepcopy(ZAS_A)
+    del raw["layers"][2]["mixer"]["mask"]  # the reader of layer 0's pages
+    model = _model(raw)
+    assert model.plan.layers[2].mixer.chunk is None and model.plan.layers[0].mixer.chunk == 17
+    assert model.cache_layout().requests[0].window is None, "the owner must keep what its reader may look back at"
 
 
 def test_a_reader_of_a_reader_is_refused():
