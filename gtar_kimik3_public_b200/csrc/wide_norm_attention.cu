@@ -131,6 +131,57 @@ __global__ void turn_back_gate_kernel(const T* __restrict__ o, const float* __re
     out[at + m + half] = from_float<T>(b);
 }
 
+// The same for bfloat16 read-outs whose halves are whole 16-byte pieces (dv a multiple of 16): a thread takes eight
+// pairs, with 16-byte loads of both halves and 32-byte loads of the cosines and sines.
+__global__ void turn_back_gate_x8_kernel(const __nv_bfloat16* __restrict__ o, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                         const int* __restrict__ tok_pos, const __nv_bfloat16* __restrict__ gate, long long ld_gate,
+                                         __nv_bfloat16* __restrict__ out, long long n8, int n_heads, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const int half = dv >> 1, pieces = half >> 3;
+    const long long th = i / pieces;
+    const int m = (int)(i - th * pieces) * 8;
+    const long long t = th / n_heads;
+    const int h = (int)(th - t * n_heads);
+    const size_t at = (size_t)th * dv + m;
+    uint4 lo = *reinterpret_cast<const uint4*>(o + at), hi = *reinterpret_cast<const uint4*>(o + at + half);
+    __nv_bfloat162* pl = reinterpret_cast<__nv_bfloat162*>(&lo);
+    __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&hi);
+    float a[8], b[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 fa = __bfloat1622float2(pl[e]), fb = __bfloat1622float2(ph[e]);
+        a[2 * e] = fa.x; a[2 * e + 1] = fa.y;
+        b[2 * e] = fb.x; b[2 * e + 1] = fb.y;
+    }
+    if (cos_t != nullptr) {
+        float c[8], s[8];
+        const size_t row = (size_t)tok_pos[t] * half + m;
+        load32(cos_t + row, c);
+        load32(sin_t + row, s);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float ra = a[e] * c[e] + b[e] * s[e], rb = b[e] * c[e] - a[e] * s[e];  // the turn by minus the angle
+            a[e] = ra;
+            b[e] = rb;
+        }
+    }
+    if (gate != nullptr) {
+        const float g = 1.f / (1.f + expf(-__bfloat162float(gate[t * ld_gate + h])));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { a[e] *= g; b[e] *= g; }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        pl[e] = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+        ph[e] = __floats2bfloat162_rn(b[2 * e], b[2 * e + 1]);
+    }
+    *reinterpret_cast<uint4*>(out + at) = lo;
+    *reinterpret_cast<uint4*>(out + at + half) = hi;
+}
+
 }  // namespace
 
 GK_EXPORT int gk_turn_back_gate(const void* o, const float* cos_t, const float* sin_t, int table_positions, int max_position,
@@ -141,6 +192,16 @@ GK_EXPORT int gk_turn_back_gate(const void* o, const float* cos_t, const float* 
     GK_REQUIRE(cos_t == nullptr || (tok_pos != nullptr && max_position < table_positions),
                "turn_back_gate: position %d is beyond the tables (%d)", max_position, table_positions);
     if (n_tokens == 0) return GK_OK;
+    const uintptr_t all = (uintptr_t)o | (uintptr_t)out | (uintptr_t)cos_t | (uintptr_t)sin_t;
+    if (dtype == GK_BF16 && dv % 16 == 0 && (all & 31) == 0) {
+        const long long n8 = n_tokens * n_heads * (dv / 16);
+        const long long blocks8 = (n8 + 255) / 256;
+        GK_REQUIRE(blocks8 < 2147483647LL, "turn_back_gate: too many elements");
+        gk_launch(turn_back_gate_x8_kernel, dim3((unsigned)blocks8), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)o, cos_t, sin_t,
+                  tok_pos, (const __nv_bfloat16*)gate, ld_gate, (__nv_bfloat16*)out, n8, n_heads, dv);
+        GK_CHECK_LAUNCH("turn_back_gate");
+        return GK_OK;
+    }
     const long long n = n_tokens * n_heads * (dv / 2);
     const long long blocks = (n + 255) / 256;
     GK_REQUIRE(blocks < 2147483647LL, "turn_back_gate: too many elements");
