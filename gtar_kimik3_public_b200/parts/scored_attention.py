@@ -164,6 +164,9 @@ class ScoredAttention(Mixer):
             rel = tensors[n["rel"]].float()
             self.distance_table = (int(rel.shape[0]), self.distance_table[1])
             self.dist_rows = distance_rows(*self.distance_table)
+            reach = min(s for s in (self.window, self.chunk, len(self.dist_rows)) if s)
+            if reach < len(self.dist_rows) and not self.keep_first:
+                self.dist_rows = self.dist_rows[:reach]  # no visible key is further back than the chunk or window is long
             self.dist_bias = rel[torch.tensor(self.dist_rows, device=rel.device)].contiguous()
         if self.sink_kind == "learned":
             self.sink = tensors[n["sink"]].float().contiguous()
