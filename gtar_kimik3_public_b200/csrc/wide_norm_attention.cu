@@ -8,7 +8,8 @@
 //                          and rotation) into the value pages.  One block per token, 32-bit arithmetic.
 //                          With v_at >= 0 the values are a projection of their own (n_kv heads of dv entries from
 //                          column v_at of the row) and go into the value pages as projected; with has_k = 0 the row
-//                          holds queries only (a layer that reads another layer's keys and values).
+//                          holds queries only (a layer that reads another layer's keys and values).  Without rotation and
+//                          with rows of whole 16-byte pieces the row is held in registers (read once, 16-byte accesses).
 //   sigmoid_gate           out = o * sigmoid(gate), the gate read from a column range of a wider row
 //   softcap                x <- cap * tanh(x / cap), in place (32-bit logits)
 //   turn_back_gate         every head's read-out o [dv] turned by MINUS the reading token's position over all of its
@@ -75,6 +76,89 @@ __global__ void __launch_bounds__(WN_THREADS) wide_norm_rope_write_kernel(
         for (int i = threadIdx.x; i < n_kv * dv; i += WN_THREADS) {
             const int hk = i / dv, j = i - hk * dv;
             v_pages[(((size_t)page * n_kv + hk) * page_size + pos % page_size) * dv + j] = from_float<TC>(to_float(row[v_at + i]));
+        }
+    }
+}
+
+// The same without rotation for rows that are whole 16-byte pieces (heads, the values' column and the row stride all
+// multiples of eight bfloat16 or four float32 entries; cache pages of the rows' type): a thread holds up to four pieces of
+// the row in registers, so that the row is read once, with 16-byte loads, and written with 16-byte stores.  A block's
+// sums are formed in a fixed order of their own (a thread its pieces in index order, a warp by shuffles, the eight
+// warps one after another), which depends on the sizes alone.
+constexpr int WN_HELD = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(WN_THREADS) wide_norm_write_vec_kernel(
+    const T* __restrict__ proj, long long ld, const float* __restrict__ w_q, const float* __restrict__ w_k,
+    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, const int* __restrict__ slots,
+    const int* __restrict__ block_table, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q, int n_kv,
+    int d, int max_pages, int page_size, float eps, int v_at, int dv, int has_k) {
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ float red[2][WN_THREADS / 32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T* row = proj + (size_t)t * ld;
+    const int nq = n_q * d, nk = has_k ? n_kv * d : 0;
+    const int q_pieces = nq / VEC, pieces = (nq + nk) / VEC;
+    uint4 held[WN_HELD];
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int h = 0; h < WN_HELD; ++h) {
+        const int c = threadIdx.x + h * WN_THREADS;
+        if (c >= pieces) break;
+        held[h] = *reinterpret_cast<const uint4*>(row + (size_t)c * VEC);
+        const T* e = reinterpret_cast<const T*>(&held[h]);
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) { const float v = to_float(e[i]); ss = fmaf(v, v, ss); }
+        if (c < q_pieces) sq += ss;
+        else sk += ss;
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if ((threadIdx.x & 31) == 0) {
+        red[0][threadIdx.x >> 5] = sq;
+        red[1][threadIdx.x >> 5] = sk;
+    }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int w = 0; w < WN_THREADS / 32; ++w) { tq += red[0][w]; tk += red[1][w]; }
+    const float rq = 1.f / sqrtf(tq / (float)nq + eps), rk = nk ? 1.f / sqrtf(tk / (float)nk + eps) : 0.f;
+    const int pos = tok_pos[t];
+    const bool write = k_pages != nullptr;
+    const int page = write ? block_table[(size_t)slots[tok_seq[t]] * max_pages + pos / page_size] : 0;
+    const int in_page = pos % page_size;
+#pragma unroll
+    for (int h = 0; h < WN_HELD; ++h) {
+        const int c = threadIdx.x + h * WN_THREADS;
+        if (c >= pieces) break;
+        const bool is_q = c < q_pieces;
+        if (!is_q && !write) continue;
+        const int at = (is_q ? c : c - q_pieces) * VEC;
+        const float r = is_q ? rq : rk;
+        const float* w = (is_q ? w_q : w_k) + at;
+        const T* e = reinterpret_cast<const T*>(&held[h]);
+        uint4 res;
+        T* o = reinterpret_cast<T*>(&res);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = from_float<T>(to_float(e[i]) * r * w[i]);
+        if (is_q) {
+            *reinterpret_cast<uint4*>(q_out + (size_t)t * nq + at) = res;
+        } else {
+            const int hk = at / d, j = at - hk * d;
+            const size_t dst = (((size_t)page * n_kv + hk) * page_size + in_page) * d + j;
+            *reinterpret_cast<uint4*>(k_pages + dst) = res;
+            if (v_at < 0) *reinterpret_cast<uint4*>(v_pages + dst) = held[h];
+        }
+    }
+    if (v_at >= 0 && nk && write) {
+        const int v_pieces = n_kv * dv / VEC;
+        for (int c = threadIdx.x; c < v_pieces; c += WN_THREADS) {
+            const int at = c * VEC, hk = at / dv, j = at - hk * dv;
+            *reinterpret_cast<uint4*>(v_pages + (((size_t)page * n_kv + hk) * page_size + in_page) * dv + j) =
+                *reinterpret_cast<const uint4*>(row + v_at + at);
         }
     }
 }
@@ -228,6 +312,20 @@ GK_EXPORT int gk_wide_norm_rope_write(const void* proj, int dtype, long long ld,
                "wide_norm_rope_write: position %d is beyond the rotation tables (%d)", max_position, table_positions);
     if (n_tokens == 0) return GK_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    {
+        const int vec = dtype == GK_BF16 ? 8 : 4;
+        const uintptr_t all = (uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)w_q | (uintptr_t)w_k;
+        const long long row_pieces = ((long long)n_q * d + (has_k ? (long long)n_kv * d : 0)) / vec;
+        if (rot == 0 && dtype == cache_dtype && d % vec == 0 && ld % vec == 0 && (all & 15) == 0 && row_pieces <= WN_THREADS * WN_HELD &&
+            (v_at < 0 || (dv % vec == 0 && v_at % vec == 0))) {
+            GK_DISPATCH_DTYPE(dtype, T, {
+                gk_launch(wide_norm_write_vec_kernel<T>, dim3(n_tokens), dim3(WN_THREADS), 0, s, (const T*)proj, ld, w_q, w_k, tok_pos, tok_seq,
+                          slots, block_table, (T*)q_out, (T*)k_pages, (T*)v_pages, n_q, n_kv, d, max_pages, page_size, eps, v_at, dv, has_k);
+            })
+            GK_CHECK_LAUNCH("wide_norm_rope_write");
+            return GK_OK;
+        }
+    }
     GK_DISPATCH_DTYPE(dtype, T, {
         GK_DISPATCH_DTYPE(cache_dtype, TC, {
             gk_launch(wide_norm_rope_write_kernel<T, TC>, dim3(n_tokens), dim3(WN_THREADS), 0, s, (const T*)proj, ld, w_q, w_k, cos_t,
