@@ -117,10 +117,16 @@ class ScoredAttention(Mixer):
 
     def tensor_specs(self):
         n, W = self.names, self.hidden_size
-        specs = {n["q"]: TensorSpec((self.n_q * self.d, W)), n["o"]: TensorSpec((W, self.n_q * self.dv))}
+        specs = {n["q"]: TensorSpec((self.n_q * self.d, W))}
         if self.own_kv:
             specs[n["k"]] = TensorSpec((self.n_kv * self.d, W))
             specs[n["v"]] = TensorSpec((self.n_kv * self.dv, W))
+        specs[n["o"]] = TensorSpec((W, self.n_q * self.dv))
+        if self.distance_bias:
+            specs[n["r1"]] = TensorSpec((self.n_q,), "vector", init=(0.3, 0.1))
+            specs[n["r2"]] = TensorSpec((self.n_q,), "vector", init=(0.5, 0.1))
+        if self.head_bias:
+            specs[n["pb"]] = TensorSpec((self.n_q,), "vector", init=(-2.0, 0.5))
         if self.wide_norm:
             specs[n["q_norm"]] = TensorSpec((self.n_q * self.d,), "vector")
             if self.own_kv:
@@ -133,11 +139,6 @@ class ScoredAttention(Mixer):
             specs[n["sink"]] = TensorSpec((self.n_q,), "vector", init=(0.0, 1.0))
         if self.head_gate:
             specs[n["g"]] = TensorSpec((self.n_q, W), init=(0.0, 0.3))
-        if self.distance_bias:
-            specs[n["r1"]] = TensorSpec((self.n_q,), "vector", init=(0.3, 0.1))
-            specs[n["r2"]] = TensorSpec((self.n_q,), "vector", init=(0.5, 0.1))
-        if self.head_bias:
-            specs[n["pb"]] = TensorSpec((self.n_q,), "vector", init=(-2.0, 0.5))
         return specs
 
     def load(self, tensors):
