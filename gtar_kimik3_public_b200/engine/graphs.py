@@ -28,6 +28,7 @@ where it first needs them.
 
 from __future__ import annotations
 
+import gc
 from collections import OrderedDict
 
 import numpy as np
@@ -158,11 +159,19 @@ class StepGraphs:
         graph = torch.cuda.CUDAGraph()
         before = set_pdl(self.use_pdl)
         count = library.launch_count
+        # Nothing may be freed on the device while a capture is under way: an engine of before that the collector finds
+        # in the middle of it takes its graphs and their memory along, and the capture is lost ("operation failed due to
+        # a previous error during capture").  So the collector runs now and rests until the capture is over.
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
         try:
             with torch.cuda.graph(graph, pool=self.pool):
                 logits = self.model.step(ctx, self.cache)
         finally:
             set_pdl(before)
+            if collecting:
+                gc.enable()
         self.launches[key] = library.launch_count - count
         library.launch_count = count
         if self.pool is None:

@@ -90,7 +90,8 @@ def zas_engine(tag: str, dtype: str, max_tokens: int, seed: int = 0, max_seqs: i
 def zas_check(tag: str, dtype: str, tokens, places, got: torch.Tensor, what: str) -> None:
     """float32: within 1e-4 of the float64 oracle on logits of size O(1).  bfloat16: against the error of the plain
     implementation with bfloat16 matrix products and bfloat16 storage between them, the largest error over the positions
-    may be at most three times the yardstick's largest and the mean error at most one and a half times its mean, each plus
+    may be at most three times the yardstick's largest and (over eight positions or more) the mean error at most one and a half
+    times its mean, each plus
     2e-3 and half a bfloat16 step at the largest logit.  (Every branch of this design is normed before its add, so a
     position where a branch nearly cancels is sensitive, and how large its error comes out depends on the order of the
     roundings: the largest error is one sample, the mean is the measure of a systematic loss.)  Only positions before the
@@ -113,5 +114,5 @@ def zas_check(tag: str, dtype: str, tokens, places, got: torch.Tensor, what: str
         slack = 2e-3 + oracle.abs().max().item() / 256
         assert err.max().item() <= 3 * yard.max().item() + slack, \
             f"{what}: bfloat16 error {err.max().item():.3e} exceeds three times the yardstick {yard.max().item():.3e}"
-        assert err.mean().item() <= 1.5 * yard.mean().item() + slack, \
+        assert len(places) < 8 or err.mean().item() <= 1.5 * yard.mean().item() + slack, \
             f"{what}: mean bfloat16 error {err.mean().item():.3e} exceeds one and a half times the yardstick's {yard.mean().item():.3e}"
