@@ -1657,7 +1657,8 @@ def heads_prepare(proj: torch.Tensor, q_at: int, k_at: int, v_at: int, n_q: int,
     require_device(proj.device)
     _check(proj, "proj", dims=2)
     T = proj.shape[0]
-    if max(q_at + n_q * d, k_at + n_k * d, v_at + n_k * dv) > proj.shape[1]:
+    reads_kv = kv is None or write_kv  # a step that writes no pages reads the queries alone (a layer that reads another's pages)
+    if max(q_at + n_q * d, (k_at + n_k * d) if reads_kv else 0, (v_at + n_k * dv) if reads_kv else 0) > proj.shape[1]:
         raise KernelError(f"heads_prepare: a projection of {proj.shape[1]} columns is too narrow for these heads")
     for name, t in (("tok_pos", tok_pos), ("tok_seq", tok_seq), ("slots", slots)):
         _check(t, name, torch.int32, 1)

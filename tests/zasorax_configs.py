@@ -76,6 +76,8 @@ ZAS_D = {
         _layer("attention", _chunked(2, 1, 20, 6, 0.35, chunk=200, far=128, rows=9), _dense(56)),
         _layer("attention_2", _turned(5, 5, 10, 14, 0.4, dims=6, base=37.0), _moe(8, 7, 3)),
         _layer("attention", _chunked(4, 1, 20, 6, 0.3, chunk=5, far=6, rows=5, kv_from=1), _dense(24)),
+        # a reader whose own row (5 query heads of 10 and 5 gates) is narrower than the keys and values it reads
+        _layer("attention_2", _turned(5, 5, 10, 14, 0.25, dims=6, base=37.0, kv_from=2), None),
     ],
 }
 
